@@ -18,7 +18,7 @@ from __future__ import annotations
 
 from dataclasses import dataclass, field
 
-from ..parts.base import LayerCache, PagedKV, SlotState
+from ..parts.base import LayerCache, PagedKV, SlotState, flatten_needs
 from .pools import OutOfPages, PagePool, SlotPool
 
 
@@ -42,8 +42,8 @@ class RequestCache:
 
 class CacheManager:
     def __init__(self, needs, *, page_size: int, num_pages, max_requests: int, poison_freed: bool = False):
-        """``needs``: per run ``("own", PagedKV|SlotState|None)`` or ``("borrow", run)``
-        (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
+        """``needs``: per run ``("own", PagedKV|SlotState|None)``, or a tuple of those (at most one
+        of them paged; states with different names), or ``("borrow", run)`` (`CausalLM.cache_needs`).  ``num_pages``: pages per group (an int for all
         groups, or one per group).  ``poison_freed`` (a debugging aid, off by default): a page
         that goes back to its pool is filled with NaN in every layer and zeroed again when it is
         handed out, so that a read of a page the reader no longer holds shows in the logits."""
@@ -57,22 +57,28 @@ class CacheManager:
         self.needs = list(needs)
         self.groups: list[CacheGroup] = []
         self.run_group: dict[int, int] = {}        # run -> group (owning runs)
-        self.state_runs: dict[int, SlotState] = {}
+        self.state_runs: dict[int, list[SlotState]] = {}
         by_need: dict[PagedKV, int] = {}
         for run, (how, what) in enumerate(self.needs):
             if how == "borrow":
                 continue
-            if isinstance(what, PagedKV):
-                if what not in by_need:
-                    by_need[what] = len(self.groups)
-                    self.groups.append(CacheGroup(what, [], None))
-                g = by_need[what]
-                self.groups[g].runs.append(run)
-                self.run_group[run] = g
-            elif isinstance(what, SlotState):
-                self.state_runs[run] = what
-            elif what is not None:
-                raise TypeError(f"run {run}: unknown cache need {what!r}")
+            for need in flatten_needs(what):
+                if isinstance(need, PagedKV):
+                    if run in self.run_group:
+                        raise TypeError(f"run {run}: a layer holds at most one paged cache")
+                    if need not in by_need:
+                        by_need[need] = len(self.groups)
+                        self.groups.append(CacheGroup(need, [], None))
+                    g = by_need[need]
+                    self.groups[g].runs.append(run)
+                    self.run_group[run] = g
+                elif isinstance(need, SlotState):
+                    have = self.state_runs.setdefault(run, [])
+                    if any(s.name == need.name for s in have):
+                        raise TypeError(f"run {run}: two states named {need.name!r}")
+                    have.append(need)
+                else:
+                    raise TypeError(f"run {run}: unknown cache need {need!r}")
         if isinstance(num_pages, int):
             num_pages = [num_pages] * len(self.groups)
         if len(num_pages) != len(self.groups):
@@ -82,8 +88,8 @@ class CacheManager:
             g.pool = PagePool(n, run=max(1, RUN_TOKENS // self.page_size))
         self.slots = SlotPool(self.max_requests)
         self.requests: dict[object, RequestCache] = {}
-        self.kv_storage = []       # per group: tensor [runs, 2, pages, nkv, page_size, hd]
-        self.state_storage = {}    # run -> tensor [slots, *shape]
+        self.kv_storage = []       # per group: tensor [runs, 2, pages, nkv, page_size, hd] (1 for 2 where keys are the values)
+        self.state_storage = {}    # (run, name) -> tensor [slots, *shape]
         self.slot_tables = {}      # name -> tensor [slots, ...] of per-request state that others own (`register_slot_table`)
         self.reuse_count = 0       # pages handed out that had been held before
         self._ever_used = [set() for _ in self.groups]
@@ -227,17 +233,18 @@ class CacheManager:
     def bytes_per_token(self, itemsize: int) -> int:
         """Sum over caching runs of 2 * kv heads * head size * itemsize
         (runtime/memory_planner.py:12-15)."""
-        return sum(len(g.runs) * 2 * g.need.num_kv_heads * g.need.head_dim * itemsize for g in self.groups)
+        return sum(len(g.runs) * (2 if g.need.values else 1) * g.need.num_kv_heads * g.need.head_dim * itemsize for g in self.groups)
 
     def state_bytes_per_request(self) -> int:
         """Bytes of fixed-size float32 state each request holds in the mixers' slots (tables that others
         register with `register_slot_table` are theirs to count)."""
         total = 0
-        for s in self.state_runs.values():
-            n = 4
-            for d in s.shape:
-                n *= int(d)
-            total += n
+        for states in self.state_runs.values():
+            for s in states:
+                n = 4
+                for d in s.shape:
+                    n *= int(d)
+                total += n
         return total
 
     def describe(self) -> list[str]:
@@ -245,7 +252,8 @@ class CacheManager:
         lines = []
         for gi, g in enumerate(self.groups):
             w = "all keys" if g.need.window is None else f"a window of {g.need.window}"
-            lines.append(f"group {gi}: {len(g.runs)} runs x {g.need.num_kv_heads} kv heads of {g.need.head_dim}, {w}")
+            what = "kv heads" if g.need.values else "latent vectors"
+            lines.append(f"group {gi}: {len(g.runs)} runs x {g.need.num_kv_heads} {what} of {g.need.head_dim}, {w}")
         if self.state_runs:
             lines.append(f"state slots: {len(self.state_runs)} runs, {self.state_bytes_per_request()} bytes per request")
         return lines
@@ -255,22 +263,25 @@ class CacheManager:
         import torch
         self.kv_storage = []
         for g in self.groups:
-            shape = (len(g.runs), 2, max(g.pool.capacity, 1), g.need.num_kv_heads, self.page_size, g.need.head_dim)
+            shape = (len(g.runs), 2 if g.need.values else 1, max(g.pool.capacity, 1), g.need.num_kv_heads, self.page_size,
+                     g.need.head_dim)
             # with the debugging aid on, pages nobody holds are NaN from the start
             fill = float("nan") if self.poison_freed else 0.0
             self.kv_storage.append(torch.full(shape, fill, dtype=dtype, device=device))
         self.state_storage = {
-            run: torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=torch.float32, device=device)
-            for run, s in self.state_runs.items()}
+            (run, s.name): torch.zeros((self.max_requests + 1,) + tuple(s.shape), dtype=torch.float32, device=device)
+            for run, states in self.state_runs.items() for s in states}
         caches: list[LayerCache] = []
         for run, (how, what) in enumerate(self.needs):
             src = what if how == "borrow" else run
+            cache = LayerCache()
             if src in self.run_group:
                 gi = self.run_group[src]
                 i = self.groups[gi].runs.index(src)
-                caches.append(LayerCache(group=gi, k=self.kv_storage[gi][i, 0], v=self.kv_storage[gi][i, 1]))
-            elif src in self.state_runs:
-                caches.append(LayerCache(state=self.state_storage[src]))
-            else:
-                caches.append(LayerCache())
+                kv = self.kv_storage[gi][i]
+                cache.group, cache.k, cache.v = gi, kv[0], kv[1 if self.groups[gi].need.values else 0]
+            if src in self.state_runs:
+                cache.states = {s.name: self.state_storage[(src, s.name)] for s in self.state_runs[src]}
+                cache.state = cache.states[self.state_runs[src][0].name]
+            caches.append(cache)
         return caches

@@ -23,7 +23,7 @@ class PartSpec:
 @dataclass(frozen=True)
 class PartEntry:
     """One part of a layer: the registry its kind is looked up in (``"mixer"``,
-    ``"feed_forward"`` or ``"norm"``), what it is built with, and the tensor-name prefix
+    ``"feed_forward"``, ``"norm"`` or ``"shift"``), what it is built with, and the tensor-name prefix
     below the layer's under which its tensors lie (empty: directly under the layer's)."""
     family: str
     spec: PartSpec
@@ -88,6 +88,7 @@ class ModelPlan:
     position: PartSpec | None      # the position encoding the mixers share
     position_name: str | None = None   # prefix of the position encoding's own tensors, if it has any
     ignored_names: tuple[str, ...] = ()  # tensors a checkpoint may carry that the model does not use (said once, in a warning)
+    embedding_scale: float = 1.0       # the looked-up rows are multiplied by it as they enter the stream
 
     def validate(self) -> None:
         from .errors import ConfigError
@@ -95,9 +96,9 @@ class ModelPlan:
             raise ConfigError("a model needs at least one layer")
         for i, layer in enumerate(self.layers):
             for role, e in layer.parts.items():
-                if e.family not in ("mixer", "feed_forward", "norm"):
+                if e.family not in ("mixer", "feed_forward", "norm", "shift"):
                     raise ConfigError(f"layers[{i}].parts[{role!r}]: unknown family {e.family!r} "
-                                      f"(mixer, feed_forward or norm)")
+                                      f"(mixer, feed_forward, norm or shift)")
         for i, e in enumerate(self.run_list):
             if not 0 <= e.layer < len(self.layers):
                 raise ConfigError(f"run_list[{i}] names layer {e.layer}, "

@@ -76,9 +76,13 @@ def read_config_json(model_dir: str) -> dict:
 
 
 def architecture_of(raw: dict) -> Architecture:
+    """The architecture a config.json names: ``architectures[0]``, or the single name under ``architecture``."""
     archs = raw.get("architectures")
+    if archs is None and isinstance(raw.get("architecture"), str):
+        archs = [raw["architecture"]]
     if not isinstance(archs, list) or not archs or not isinstance(archs[0], str):
-        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names")
+        raise ConfigError("config.json: key 'architectures' must be a non-empty list of names "
+                          "(or 'architecture' a single name)")
     return get_architecture(archs[0])
 
 

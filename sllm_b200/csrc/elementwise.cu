@@ -37,11 +37,11 @@ int num_sms() {
 }
 
 // ---------------------------------------------------------------------------
-// out[t, :] = float(table[ids[t], :])      (kernels/cuda/kernels.cu:770-787 does one row)
+// out[t, :] = float(table[ids[t], :]) * scale      (kernels/cuda/kernels.cu:770-787 does one row)
 // ---------------------------------------------------------------------------
 template <typename TW>
 __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __restrict__ ids,
-                                    float* __restrict__ out, int H, int V) {
+                                    float* __restrict__ out, int H, int V, float scale) {
   pdl_launch_dependents();       // a short kernel: the successor may be set up behind it
   pdl_wait();
   const int t = blockIdx.x;
@@ -49,7 +49,7 @@ __global__ void embed_gather_kernel(const TW* __restrict__ table, const int* __r
   id = id < 0 ? 0 : (id >= V ? V - 1 : id);     // the host validates ids; never read outside the table
   const TW* row = table + (size_t)id * H;
   float* o = out + (size_t)t * H;
-  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]);
+  for (int i = threadIdx.x; i < H; i += blockDim.x) o[i] = to_f32(row[i]) * scale;
 }
 
 // ---------------------------------------------------------------------------
@@ -376,14 +376,14 @@ SLLM_EXPORT const char* sllm_last_error() { return g_error; }
 SLLM_EXPORT int sllm_num_sms() { return sllm::num_sms(); }
 
 SLLM_EXPORT int sllm_embed_gather(const void* table, int table_dtype, const int* ids, float* out, int T, int H,
-                                  int V, cudaStream_t stream) {
+                                  int V, float scale, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && H > 0 && V > 0, "embed_gather: bad sizes T=%d H=%d V=%d", T, H, V);
   if (T == 0) return SLLM_OK;
   const int threads = H >= 1024 ? 256 : 128;
   if (table_dtype == SLLM_F32)
-    launch_kernel(embed_gather_kernel<float>, T, threads, 0, stream, (const float*)table, ids, out, H, V);
+    launch_kernel(embed_gather_kernel<float>, T, threads, 0, stream, (const float*)table, ids, out, H, V, scale);
   else if (table_dtype == SLLM_BF16)
-    launch_kernel(embed_gather_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, H, V);
+    launch_kernel(embed_gather_kernel<__nv_bfloat16>, T, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, H, V, scale);
   else
     SLLM_REQUIRE(false, "embed_gather: unknown dtype %d", table_dtype);
   return launch_status("embed_gather");

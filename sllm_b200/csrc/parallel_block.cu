@@ -1,0 +1,216 @@
+// Memory-bound kernels of a "parallel" block (one norm whose output both the mixer and the feed-forward
+// read) and of an input with sinusoidal positions:
+//   * a sinusoidal position vector added to the float32 stream;
+//   * the pending terms added into the stream and, per row and group, 1/sqrt(mean square + eps) of the
+//     stream (an RMS norm taken over `groups` equal consecutive parts of the vector);
+//   * that norm applied (times a gain), with an optional token shift: the mixer's input is the row blended
+//     with the previous token's normed row, which for the first token of a portion comes from the
+//     request's state slot; the slot then receives the portion's last normed row;
+//   * act(gate) * up of a gate|up product, act = SiLU or the tanh form of GELU;
+//   * an activation over some columns of a float32 product.
+// All arithmetic in float32; the stream, the gains, the state and the reciprocal roots are float32.
+#include "common.cuh"
+
+namespace sllm {
+
+// stream[t, 2i] += sin(p * f_i), stream[t, 2i+1] += cos(p * f_i), p = positions[t], f = inv_freq[i].
+// The angle is a float32 product of the float32 position and the float32 frequency; sinf and cosf are
+// the accurate forms (their argument reduction is exact for angles of this size).
+__global__ void add_sinusoid_kernel(float* __restrict__ stream, const int* __restrict__ positions,
+                                    const float* __restrict__ inv_freq, int W) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const float p = (float)positions[t];
+  float* row = stream + (size_t)t * W;
+  for (int i = threadIdx.x; i < W / 2; i += blockDim.x) {
+    const float ang = p * inv_freq[i];
+    float s, c;
+    sincosf(ang, &s, &c);
+    row[2 * i] += s;
+    row[2 * i + 1] += c;
+  }
+}
+
+// Row t of the stream takes the pending terms (each a stack of `parts` partial sums, float32); then, if
+// rinv is given, rinv[t, g] = 1 / sqrt(mean(stream[t, group g]^2) + eps).  A warp owns a group (warps take
+// groups in turn) and sums it in an order that depends on the group's size only.
+__global__ void add_group_ssq_kernel(float* __restrict__ stream, const float* __restrict__ d0, int parts0, size_t stride0,
+                                     const float* __restrict__ d1, int parts1, size_t stride1,
+                                     float* __restrict__ rinv, int W, int groups, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float* row = stream + (size_t)t * W;
+  if (d0 != nullptr || d1 != nullptr) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      float v = row[i];
+      if (d0 != nullptr)
+        for (int p = 0; p < parts0; ++p) v += d0[p * stride0 + (size_t)t * W + i];
+      if (d1 != nullptr)
+        for (int p = 0; p < parts1; ++p) v += d1[p * stride1 + (size_t)t * W + i];
+      row[i] = v;
+    }
+    __syncthreads();       // the block's own writes are read back below
+  }
+  if (rinv == nullptr) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int gs = W / groups;
+  for (int g = warp; g < groups; g += nw) {
+    const float* x = row + (size_t)g * gs;
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) rinv[(size_t)t * groups + g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
+}
+
+// h[t, i] = stream[t, i] * rinv[t, g(i)] * gain[i]                      -> out_h (if given)
+// hs[t, i] = h + (h_prev - h) * mix[i]                                   -> out_hs (if mix is given)
+// h_prev is the normed row t-1 of the same request's portion, or state[slot] for the portion's first
+// token; the block of that first token then writes the portion's last normed row to state[slot] (each
+// thread reads its channels of the slot before it writes them; no other block touches the slot).
+template <typename TO>
+__global__ void group_norm_shift_kernel(const float* __restrict__ stream, const float* __restrict__ rinv,
+                                        const float* __restrict__ gain, const float* __restrict__ mix,
+                                        float* __restrict__ state, const int* __restrict__ seq_of_token,
+                                        const int* __restrict__ q_start, const int* __restrict__ state_slots,
+                                        TO* __restrict__ out_h, TO* __restrict__ out_hs, int W, int groups) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int gs = W / groups;
+  const float* row = stream + (size_t)t * W;
+  const float* ri = rinv + (size_t)t * groups;
+  if (mix == nullptr) {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) out_h[(size_t)t * W + i] = from_f32<TO>(row[i] * ri[i / gs] * gain[i]);
+    return;
+  }
+  const int s = seq_of_token[t];
+  const int first_t = q_start[s], last_t = q_start[s + 1] - 1;
+  const bool first = t == first_t;
+  float* slot = state + (size_t)state_slots[s] * W;
+  const float* prow = row - W;
+  const float* pri = ri - groups;
+  const float* lrow = stream + (size_t)last_t * W;
+  const float* lri = rinv + (size_t)last_t * groups;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const int g = i / gs;
+    const float w = gain[i];
+    const float h = row[i] * ri[g] * w;
+    float hp;
+    if (first) {
+      hp = slot[i];
+      slot[i] = lrow[i] * lri[g] * w;
+    } else {
+      hp = prow[i] * pri[g] * w;
+    }
+    if (out_h != nullptr) out_h[(size_t)t * W + i] = from_f32<TO>(h);
+    out_hs[(size_t)t * W + i] = from_f32<TO>(h + (hp - h) * mix[i]);
+  }
+}
+
+__device__ __forceinline__ float act_silu(float z) { return z / (1.0f + expf(-z)); }
+__device__ __forceinline__ float act_gelu_tanh(float z) {
+  return 0.5f * z * (1.0f + tanhf(0.7978845608028654f * (z + 0.044715f * z * z * z)));
+}
+
+// out[t, i] = act(gate) * up; gate and up alternate along a row of gu in blocks of `interleave` columns
+// (interleave == I: all gates, then all ups).
+template <typename TI, typename TO, int ACT>
+__global__ void act_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int interleave) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t t = blockIdx.y;
+  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+    const int b = i / interleave, o = i % interleave;
+    const TI* p = gu + t * 2 * I + (size_t)b * 2 * interleave + o;
+    const float g = to_f32(p[0]), u = to_f32(p[interleave]);
+    out[t * I + i] = from_f32<TO>((ACT == 0 ? act_silu(g) : act_gelu_tanh(g)) * u);
+  }
+}
+
+// out[t, j] = tanh(x[t, col0 + j]), j < n; x float32 with row stride ld.
+template <typename TO>
+__global__ void tanh_cols_kernel(const float* __restrict__ x, int ld, int col0, int n, TO* __restrict__ out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t total = (size_t)T * n;
+  for (size_t e = (size_t)blockIdx.x * blockDim.x + threadIdx.x; e < total; e += (size_t)gridDim.x * blockDim.x) {
+    const size_t t = e / n;
+    const int j = (int)(e % n);
+    out[e] = from_f32<TO>(tanhf(x[t * ld + col0 + j]));
+  }
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_add_sinusoid(float* stream, const int* positions, const float* inv_freq, int T, int W,
+                                  cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && W > 0 && W % 2 == 0, "add_sinusoid: the width %d must be even", W);
+  if (T == 0) return SLLM_OK;
+  launch_kernel(add_sinusoid_kernel, T, W >= 2048 ? 256 : 128, 0, stream_, stream, positions, inv_freq, W);
+  return launch_status("add_sinusoid");
+}
+
+SLLM_EXPORT int sllm_add_group_ssq(float* stream, const float* d0, int parts0, size_t stride0, const float* d1, int parts1,
+                                   size_t stride1, float* rinv, int T, int W, int groups, float eps, cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && W > 0 && groups > 0 && W % groups == 0, "add_group_ssq: %d groups do not divide the width %d", groups, W);
+  SLLM_REQUIRE((d0 == nullptr || parts0 >= 1) && (d1 == nullptr || parts1 >= 1), "add_group_ssq: bad parts");
+  if (T == 0) return SLLM_OK;
+  launch_kernel(add_group_ssq_kernel, T, 256, 0, stream_, stream, d0, parts0, stride0, d1, parts1, stride1, rinv, W, groups, eps);
+  return launch_status("add_group_ssq");
+}
+
+SLLM_EXPORT int sllm_group_norm_shift(const float* stream, const float* rinv, const float* gain, const float* mix, float* state,
+                                      const int* seq_of_token, const int* q_start, const int* state_slots, void* out_h,
+                                      void* out_hs, int out_dtype, int T, int W, int groups, cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && W > 0 && groups > 0 && W % groups == 0, "group_norm_shift: %d groups do not divide the width %d", groups, W);
+  SLLM_REQUIRE(mix != nullptr ? (state && seq_of_token && q_start && state_slots && out_hs) : (out_h != nullptr),
+               "group_norm_shift: a shift needs its state, the batch's description and an output; a plain norm needs an output");
+  if (T == 0) return SLLM_OK;
+  const int threads = W >= 2048 ? 256 : 128;
+  if (out_dtype == SLLM_F32)
+    launch_kernel(group_norm_shift_kernel<float>, T, threads, 0, stream_, stream, rinv, gain, mix, state, seq_of_token, q_start,
+                  state_slots, (float*)out_h, (float*)out_hs, W, groups);
+  else if (out_dtype == SLLM_BF16)
+    launch_kernel(group_norm_shift_kernel<__nv_bfloat16>, T, threads, 0, stream_, stream, rinv, gain, mix, state, seq_of_token,
+                  q_start, state_slots, (__nv_bfloat16*)out_h, (__nv_bfloat16*)out_hs, W, groups);
+  else
+    SLLM_REQUIRE(false, "group_norm_shift: unknown dtype %d", out_dtype);
+  return launch_status("group_norm_shift");
+}
+
+SLLM_EXPORT int sllm_act_mul(const void* gu, int in_dtype, void* out, int out_dtype, int T, int I, int interleave, int act,
+                             cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && I > 0 && interleave > 0 && I % interleave == 0, "act_mul: bad sizes T=%d I=%d interleave=%d", T, I, interleave);
+  SLLM_REQUIRE(act == 0 || act == 1, "act_mul: activation %d is neither 0 (silu) nor 1 (gelu_tanh)", act);
+  if (T == 0) return SLLM_OK;
+  const dim3 grid((unsigned)((I + 255) / 256 > 64 ? 64 : (I + 255) / 256), (unsigned)T);
+  SLLM_REQUIRE(T <= 65535, "act_mul: more than 65535 rows in one launch");
+#define SLLM_ACT_MUL(TI, TO)                                                                                              \
+  do {                                                                                                                    \
+    if (act == 0) launch_kernel(act_mul_kernel<TI, TO, 0>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave); \
+    else launch_kernel(act_mul_kernel<TI, TO, 1>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);          \
+  } while (0)
+  if (in_dtype == SLLM_F32 && out_dtype == SLLM_F32) SLLM_ACT_MUL(float, float);
+  else if (in_dtype == SLLM_F32 && out_dtype == SLLM_BF16) SLLM_ACT_MUL(float, __nv_bfloat16);
+  else if (in_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) SLLM_ACT_MUL(__nv_bfloat16, __nv_bfloat16);
+  else SLLM_REQUIRE(false, "act_mul: dtypes %d -> %d", in_dtype, out_dtype);
+#undef SLLM_ACT_MUL
+  return launch_status("act_mul");
+}
+
+SLLM_EXPORT int sllm_tanh_cols(const float* x, int ld, int col0, int n, void* out, int out_dtype, int T, cudaStream_t stream_) {
+  SLLM_REQUIRE(T >= 0 && n > 0 && col0 >= 0 && col0 + n <= ld, "tanh_cols: columns %d..%d of %d", col0, col0 + n, ld);
+  if (T == 0) return SLLM_OK;
+  const size_t total = (size_t)T * n;
+  const int blocks = (int)((total + 255) / 256 > 4096 ? 4096 : (total + 255) / 256);
+  if (out_dtype == SLLM_F32) launch_kernel(tanh_cols_kernel<float>, blocks, 256, 0, stream_, x, ld, col0, n, (float*)out, T);
+  else if (out_dtype == SLLM_BF16)
+    launch_kernel(tanh_cols_kernel<__nv_bfloat16>, blocks, 256, 0, stream_, x, ld, col0, n, (__nv_bfloat16*)out, T);
+  else SLLM_REQUIRE(false, "tanh_cols: unknown dtype %d", out_dtype);
+  return launch_status("tanh_cols");
+}

@@ -33,9 +33,9 @@ def resident_bytes(model: CausalLM) -> int:
     total = 0
     for s in model.tensor_specs():
         n = 1
-        for d in s.shape:
+        for d in (s.shape if all(d is not None for d in s.shape) else (s.shape_default or ())):
             n *= int(d)
-        total += n * (4 if s.role in ("gain", "bias") else itemsize)
+        total += n * (4 if s.role in ("gain", "bias", "mix") else itemsize)
     return total
 
 
@@ -79,12 +79,15 @@ def build_random_model(config: dict, seed: int, dtype="bfloat16", device="cuda:0
 
     def fetch(name):
         s = specs[name]
+        shape = s.concrete_shape()
         if s.role == "gain":
-            t = torch.ones(s.shape, dtype=torch.float32, device=device)
+            t = torch.ones(shape, dtype=torch.float32, device=device)
             if gain_std:
-                t += gain_std * torch.randn(s.shape, generator=gen, device=device)
+                t += gain_std * torch.randn(shape, generator=gen, device=device)
             return t
-        t = torch.empty(s.shape, dtype=dt if s.role != "bias" else torch.float32, device=device)
+        if s.role == "mix":
+            return torch.empty(shape, dtype=torch.float32, device=device).uniform_(0.05, 0.95, generator=gen)
+        t = torch.empty(shape, dtype=dt if s.role != "bias" else torch.float32, device=device)
         t.normal_(0.0, std, generator=gen)
         return t
 

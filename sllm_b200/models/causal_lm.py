@@ -9,12 +9,13 @@ import torch
 
 from .. import ops
 from ..config.plan import ModelPlan
-from ..parts import standard as _standard  # noqa: F401  (registers the standard parts)
-from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS,
-                          LayerCache, OwedNorm, StepContext, TensorSpec)
+from ..parts import delta_rule as _delta_rule, latent_attention as _latent, parallel as _parallel  # noqa: F401
+from ..parts import standard as _standard  # noqa: F401  (each import registers its parts)
+from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHIFTS,
+                          LayerCache, OwedNorm, StepContext, TensorSpec, join_name)
 
 
-FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS}
+FAMILIES = {"mixer": MIXERS, "feed_forward": FEED_FORWARDS, "norm": NORMS, "shift": SHIFTS}
 
 
 class Layer:
@@ -35,7 +36,7 @@ class Layer:
 
     def named_parts(self):
         s = self.spec
-        return [(f"{s.prefix}.{e.name}" if e.name else s.prefix, self.parts[role]) for role, e in s.parts.items()]
+        return [(join_name(s.prefix, e.name), self.parts[role]) for role, e in s.parts.items()]
 
 
 class CausalLM:
@@ -80,7 +81,7 @@ class CausalLM:
         p = self.plan
         self.embedding = fetch(p.embedding_name).to(device=self.device, dtype=self.dtype).contiguous()
         for prefix, part in self._named_parts():
-            part.bind(lambda rel, _p=prefix: fetch(f"{_p}.{rel}"))
+            part.bind(lambda rel, _p=prefix: fetch(join_name(_p, rel)))
         if p.head_name is None:
             self.head = self.embedding
         else:
@@ -111,7 +112,7 @@ class CausalLM:
     def forward(self, step: StepContext, caches: list[LayerCache]) -> torch.Tensor:
         """Run the batch's tokens through every entry of the run list and return
         float32 logits ``[R, V]`` at ``step.logit_rows``."""
-        residual = ops.embed_gather(self.embedding, step.token_ids)       # [T, H] float32
+        residual = ops.embed_gather(self.embedding, step.token_ids, self.plan.embedding_scale)       # [T, H] float32
         if self.position is not None:
             self.position.on_embedding(residual, step)
         delta = None

@@ -61,12 +61,158 @@ def _stream():
     return torch.cuda.current_stream().cuda_stream
 
 
-def embed_gather(table: torch.Tensor, ids: torch.Tensor) -> torch.Tensor:
-    """float32 ``[T, H]`` rows of ``table`` (``[V, H]``) at int32 ``ids``."""
+def embed_gather(table: torch.Tensor, ids: torch.Tensor, scale: float = 1.0) -> torch.Tensor:
+    """float32 ``[T, H]`` rows of ``table`` (``[V, H]``) at int32 ``ids``, times ``scale``."""
     _chk(table, ids)
     T, (V, H) = ids.numel(), table.shape
     out = torch.empty((T, H), dtype=torch.float32, device=table.device)
-    call("sllm_embed_gather", _p(table), _dt(table), _p(ids), _p(out), T, H, V, _stream())
+    call("sllm_embed_gather", _p(table), _dt(table), _p(ids), _p(out), T, H, V, float(scale), _stream())
+    return out
+
+
+# ---- a stream with sinusoidal positions, a norm in groups, a token shift ----------------------------
+
+def add_sinusoid_(stream: torch.Tensor, positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """``stream[t, 2i] += sin(p_t f_i)``, ``stream[t, 2i+1] += cos(p_t f_i)`` in place; the angle is a float32 product."""
+    _chk(stream, positions, inv_freq)
+    T, W = stream.shape
+    if stream.dtype != torch.float32 or inv_freq.dtype != torch.float32 or inv_freq.numel() != W // 2:
+        raise KernelError("add_sinusoid_: a float32 stream of even width and width/2 float32 frequencies")
+    call("sllm_add_sinusoid", _p(stream), _p(positions), _p(inv_freq), T, W, _stream())
+    return stream
+
+
+def _term(t):
+    """(pointer, parts, stride) of a pending term: float32 ``[T, W]`` or a stack of partial sums ``[parts, T, W]``."""
+    if t is None:
+        return None, 0, 0
+    if t.dtype != torch.float32:
+        raise KernelError("a pending term of the stream is float32")
+    return (_p(t), t.shape[0], t.shape[1] * t.shape[2]) if t.dim() == 3 else (_p(t), 1, 0)
+
+
+def add_group_ssq(stream: torch.Tensor, terms, groups: int, eps: float, want_rinv: bool = True):
+    """Add up to two pending ``terms`` into the float32 ``stream`` in place and return, per row and group of
+    ``width / groups`` consecutive channels, ``1 / sqrt(mean square + eps)`` as float32 ``[T, groups]`` (None if
+    not wanted: a plain addition)."""
+    terms = [t for t in (terms or ()) if t is not None]
+    if len(terms) > 2:
+        raise KernelError("add_group_ssq: at most two pending terms")
+    _chk(stream, *terms)
+    T, W = stream.shape
+    if stream.dtype != torch.float32:
+        raise KernelError("add_group_ssq: the stream is float32")
+    for t in terms:
+        if tuple(t.shape[-2:]) != (T, W):
+            raise KernelError(f"add_group_ssq: a term {tuple(t.shape)} does not fit the stream {(T, W)}")
+    rinv = torch.empty((T, groups), dtype=torch.float32, device=stream.device) if want_rinv else None
+    d0 = _term(terms[0] if terms else None)
+    d1 = _term(terms[1] if len(terms) > 1 else None)
+    call("sllm_add_group_ssq", _p(stream), *d0, *d1, _p(rinv), T, W, int(groups), float(eps), _stream())
+    return rinv
+
+
+def group_norm_shift(stream, rinv, gain, out_dtype, *, mix=None, state=None, step=None, want_plain: bool = True):
+    """The norm in groups applied: ``h = stream * rinv[group] * gain`` in ``out_dtype``.  With ``mix``: also the
+    mixer's input ``hs = h + (h_prev - h) * mix``, ``h_prev`` the same request's row before (for the first token
+    of its portion, the request's row of ``state`` ``[slots, W]``, which then receives the portion's last ``h``).
+    Returns ``h``, or ``(h, hs)`` (``h`` None if not wanted)."""
+    _chk(stream, rinv, gain, mix, state)
+    T, W = stream.shape
+    groups = rinv.shape[1]
+    h = torch.empty((T, W), dtype=out_dtype, device=stream.device) if (want_plain or mix is None) else None
+    if mix is None:
+        call("sllm_group_norm_shift", _p(stream), _p(rinv), _p(gain), None, None, None, None, None, _p(h), None,
+             _dtc(out_dtype), T, W, groups, _stream())
+        return h
+    hs = torch.empty((T, W), dtype=out_dtype, device=stream.device)
+    call("sllm_group_norm_shift", _p(stream), _p(rinv), _p(gain), _p(mix), _p(state), _p(step.seq_of_token), _p(step.q_start),
+         _p(step.state_slots), _p(h), _p(hs), _dtc(out_dtype), T, W, groups, _stream())
+    return h, hs
+
+
+ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+
+
+def act_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype, act: str) -> torch.Tensor:
+    """``act(gate) * up`` of ``gu [T, 2I]`` whose columns alternate between gate and up in blocks of
+    ``interleave`` (``interleave == I``: all gates, then all ups); ``act`` is ``silu`` or ``gelu_tanh``."""
+    _chk(gu)
+    T, two_i = gu.shape
+    I = two_i // 2
+    out = torch.empty((T, I), dtype=out_dtype, device=gu.device)
+    call("sllm_act_mul", _p(gu), _dt(gu), _p(out), _dtc(out_dtype), T, I, int(interleave), ACTIVATIONS[act], _stream())
+    return out
+
+
+def tanh_cols(x: torch.Tensor, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
+    """``tanh(x[:, col0:col0+n])`` of a float32 product, in ``out_dtype``."""
+    _chk(x)
+    T, ld = x.shape
+    if x.dtype != torch.float32:
+        raise KernelError("tanh_cols: a float32 product")
+    out = torch.empty((T, n), dtype=out_dtype, device=x.device)
+    call("sllm_tanh_cols", _p(x), ld, int(col0), int(n), _p(out), _dtc(out_dtype), T, _stream())
+    return out
+
+
+# ---- the generalized delta rule -----------------------------------------------------------------------
+
+def delta_rule_supports(dk: int, dv: int) -> bool:
+    return 1 <= dk <= 256 and dv >= 1
+
+
+def delta_rule(proj, offs, decay, a_bias, state, step, heads: int, dk: int, dv: int) -> torch.Tensor:
+    """The recurrence over the step's tokens, request by request in token order, from and into the
+    requests' rows of ``state`` (float32 ``[slots, heads, dk, dv]``).  ``proj`` is a float32 product ``[T, ld]``
+    whose columns ``offs = (r, k, v, a)`` hold receptance, key, value and removal logits; ``decay`` float32
+    ``[T, heads*dk]`` holds decay logits; ``a_bias`` float32 ``[heads*dk]``.  Returns ``o`` float32 ``[T, heads*dv]``."""
+    _chk(proj, decay, a_bias, state)
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or decay.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("delta_rule: everything that enters the recurrence is float32")
+    if tuple(decay.shape) != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError(f"delta_rule: decay {tuple(decay.shape)} or state {tuple(state.shape)} does not fit {heads} heads of {dk}x{dv}")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    off_r, off_k, off_v, off_a = (int(o) for o in offs)
+    call("sllm_delta_rule", _p(proj), ld, off_r, off_k, off_v, off_a, _p(decay), _p(a_bias), _p(state), _p(step.q_start),
+         _p(step.state_slots), _p(out), step.num_seqs, heads, dk, dv, _stream())
+    return out
+
+
+def delta_out(o, gain, proj, off_g: int, eps: float, heads: int, dv: int, out_dtype) -> torch.Tensor:
+    """Each head's ``o`` over its root mean square, times ``gain``, times ``sigmoid`` of the gate logits (columns
+    ``off_g`` of ``proj``), in ``out_dtype``."""
+    _chk(o, gain, proj)
+    T = o.shape[0]
+    out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
+    call("sllm_delta_out", _p(o), _p(gain), _p(proj), proj.shape[1], int(off_g), float(eps), _p(out), _dtc(out_dtype), T, heads, dv,
+         _stream())
+    return out
+
+
+# ---- latent attention ------------------------------------------------------------------------------------
+
+def latent_write(proj, off: int, rank: int, gain, eps: float, slot_mapping, cache) -> None:
+    """Columns ``off .. off+rank`` of the float32 product, over their root mean square, times ``gain``: each
+    token's latent, written to its place in the paged ``cache`` ``[pages, 1, page_size, rank]`` (skipped where the
+    slot is -1)."""
+    _chk(proj, gain, slot_mapping, cache)
+    if proj.dtype != torch.float32 or cache.shape[1] != 1 or cache.shape[3] != rank:
+        raise KernelError("latent_write: a float32 product and a cache [pages, 1, page_size, rank]")
+    call("sllm_latent_write", _p(proj), proj.shape[1], int(off), int(rank), _p(gain), float(eps), _p(slot_mapping), _p(cache),
+         _dt(cache), proj.shape[0], _stream())
+
+
+def head_linear(x, xoff: int, w, out_dtype, *, gate=None, goff: int = 0) -> torch.Tensor:
+    """A product per head: ``out[t, h, :] = w[h] @ x[t, xoff + h*din : xoff + (h+1)*din]`` with ``w [H, dout, din]``,
+    times ``sigmoid(gate[t, goff + h])`` if ``gate`` (a float32 product) is given.  ``[T, H*dout]`` in ``out_dtype``."""
+    _chk(x, w, gate)
+    T, ldx = x.shape
+    H, dout, din = w.shape
+    out = torch.empty((T, H * dout), dtype=out_dtype, device=x.device)
+    call("sllm_head_linear", _p(x), _dt(x), ldx, int(xoff), _p(w), _dt(w), _p(out), _dtc(out_dtype), _p(gate),
+         gate.shape[1] if gate is not None else 0, int(goff), T, H, din, dout, _stream())
     return out
 
 

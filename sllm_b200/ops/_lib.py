@@ -39,7 +39,21 @@ def _declare(L):
     L.sllm_num_sms.restype = c_int
     L.sllm_num_sms.argtypes = []
     sigs = {
-        "sllm_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+        "sllm_embed_gather": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_float, c_void_p],
+        "sllm_add_sinusoid": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "sllm_add_group_ssq": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int, c_size_t, c_void_p, c_int, c_int, c_int, c_float,
+                               c_void_p],
+        "sllm_group_norm_shift": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                  c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_act_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_tanh_cols": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
+        "sllm_delta_rule_supports": [c_int, c_int],
+        "sllm_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                            c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_latent_write": [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
+        "sllm_head_linear": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
+                             c_int, c_int, c_void_p],
         "sllm_add_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_size_t, c_void_p, c_float, c_void_p, c_int,
                              c_int, c_int, c_void_p],
         "sllm_silu_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_void_p],

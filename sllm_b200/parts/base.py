@@ -47,17 +47,40 @@ import torch
 class TensorSpec:
     """A tensor a part expects.  ``role`` drives random initialisation
     (matrix, bias, gain, embedding); optional tensors that only make sense
-    together share a ``together`` key."""
+    together share a ``together`` key.  An empty ``name`` is the tensor that carries
+    the part's own prefix as its whole name.  A dimension of ``shape`` that is None is
+    read from the checkpoint (a size the configuration does not give); random
+    initialisation then takes ``shape_default``."""
     name: str
     shape: tuple
     role: str = "matrix"
     optional: bool = False
     together: str | None = None
+    shape_default: tuple | None = None
 
     def prefixed(self, prefix: str) -> "TensorSpec":
-        name = f"{prefix}.{self.name}" if prefix else self.name
+        name = join_name(prefix, self.name)
         tg = f"{prefix}.{self.together}" if (prefix and self.together) else self.together
-        return TensorSpec(name, self.shape, self.role, self.optional, tg)
+        return TensorSpec(name, self.shape, self.role, self.optional, tg, self.shape_default)
+
+    def fits(self, shape) -> bool:
+        shape = tuple(shape)
+        return len(shape) == len(self.shape) and all(w is None or int(w) == int(g) for w, g in zip(self.shape, shape))
+
+    def concrete_shape(self) -> tuple:
+        """The shape to draw random values in."""
+        if all(d is not None for d in self.shape):
+            return tuple(self.shape)
+        if self.shape_default is None:
+            raise ValueError(f"{self.name}: a size read from the checkpoint has no default to draw random weights with")
+        return tuple(self.shape_default)
+
+
+def join_name(prefix: str, name: str) -> str:
+    """A part's tensor under the part's prefix; an empty name is the prefix itself."""
+    if not prefix:
+        return name
+    return f"{prefix}.{name}" if name else prefix
 
 
 # ---- what a mixer may ask of the cache manager ------------------------------
@@ -65,16 +88,35 @@ class TensorSpec:
 @dataclass(frozen=True)
 class PagedKV:
     """Keys and values per token, in pages.  ``window``: only the last
-    ``window`` positions are ever read again (None: all)."""
+    ``window`` positions are ever read again (None: all).  ``values`` false: one vector
+    per token serves as key and as value (a cached latent); the run's `LayerCache.v` is
+    then its ``k``, and nothing is stored twice."""
     num_kv_heads: int
     head_dim: int
     window: int | None = None
+    values: bool = True
 
 
 @dataclass(frozen=True)
 class SlotState:
-    """A fixed-size float32 state per request, zeroed when the request starts."""
+    """A fixed-size float32 state per request, zeroed when the request starts.  A layer that
+    keeps several (a recurrent mixer's matrix and a block's previous token) names them; each is
+    found under its name in `LayerCache.states`."""
     shape: tuple
+    name: str = "state"
+
+
+def flatten_needs(need) -> list:
+    """What a layer asks of the cache manager as a flat list: None, one need, or a tuple of needs
+    (at most one of them paged)."""
+    if need is None:
+        return []
+    if isinstance(need, (tuple, list)):
+        out = []
+        for n in need:
+            out.extend(flatten_needs(n))
+        return out
+    return [need]
 
 
 # ---- the batch a step runs --------------------------------------------------
@@ -120,7 +162,8 @@ class LayerCache:
     group: int | None = None            # index into StepContext.groups (paged)
     k: torch.Tensor | None = None       # [num_pages, nkv, page_size, hd]
     v: torch.Tensor | None = None
-    state: torch.Tensor | None = None   # [num_slots, *shape] float32
+    state: torch.Tensor | None = None   # [num_slots, *shape] float32 (the first of `states`)
+    states: dict = field(default_factory=dict)   # name -> [num_slots, *shape] float32
 
 
 # ---- a norm whose division is still owed --------------------------------------------
@@ -185,6 +228,7 @@ FEED_FORWARDS = Registry("feed-forward")
 NORMS = Registry("norm")
 POSITIONS = Registry("position encoding")
 BLOCKS = Registry("block")
+SHIFTS = Registry("token shift")
 
 
 class Part:

@@ -1,0 +1,204 @@
+"""Parts of a "parallel" layer: an RMS norm taken in groups, a sinusoidal position vector added to the
+input, a gated feed-forward with biases and a choice of activation, and the block that lets the mixer
+and the feed-forward read ONE norm's output and adds both terms to the stream, with an optional token
+shift in front of the mixer.  Each takes its sizes and constants as parameters; none names a model.
+
+All arithmetic runs in the kernels behind `sllm_b200.ops`.
+"""
+
+from __future__ import annotations
+
+import numpy as np
+import torch
+
+from .. import ops
+from .base import (BLOCKS, FEED_FORWARDS, NORMS, POSITIONS, SHIFTS, FeedForward, Norm, OwedNorm, Part,
+                   PositionEncoding, SlotState, TensorSpec, flatten_needs)
+from .standard import Linear
+
+
+@NORMS.register("group_rmsnorm")
+class GroupRMSNorm(Norm):
+    """The vector in ``groups`` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps); the
+    whole times a plain gain.  float32 on the float32 stream.  ``groups`` = 1 is the ordinary RMS norm.  The gain
+    is the tensor that carries the norm's own name."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.size = int(params["size"])
+        self.groups = int(params.get("groups", 1))
+        self.eps = float(params["eps"])
+        if self.groups < 1 or self.size % self.groups:
+            raise ValueError(f"group_rmsnorm: {self.groups} groups do not divide {self.size}")
+        self.weight = None
+
+    def tensor_specs(self):
+        return [TensorSpec("", (self.size,), role="gain")]
+
+    def bind(self, fetch):
+        self.weight = self._f32(fetch(""))
+
+    def sum_squares(self, residual, terms):
+        """Add the pending terms into the stream; the reciprocal roots per row and group."""
+        return ops.add_group_ssq(residual, terms, self.groups, self.eps)
+
+    def add_norm(self, residual, delta):
+        rinv = self.sum_squares(residual, pending_terms(delta))
+        return ops.group_norm_shift(residual, rinv, self.weight, self.dtype)
+
+    def weight_bytes(self):
+        return self.size * 4
+
+
+def pending_terms(delta) -> list:
+    """The terms a block before has left to be added: nothing, one tensor (possibly a stack of partial sums), a
+    sequence of such, or a norm still owed (whose stream is complete: nothing to add)."""
+    if delta is None or isinstance(delta, OwedNorm):
+        return []
+    if isinstance(delta, (tuple, list)):
+        return [d for d in delta if d is not None]
+    return [delta]
+
+
+@POSITIONS.register("sinusoidal")
+class Sinusoidal(PositionEncoding):
+    """A position vector added to the input: channels come in pairs (sin, cos) of the angle p * f_i, with f_i =
+    base^(-2i/width) for pair i of position p.  The frequencies are computed once in float64 and kept in float32; the angle
+    is a float32 product.  No table over positions, so no limit on them."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.width = int(params["width"])
+        self.base = float(params.get("base", 10000.0))
+        if self.width % 2:
+            raise ValueError(f"sinusoidal positions need an even width, got {self.width}")
+        f = self.base ** (-2.0 * np.arange(self.width // 2, dtype=np.float64) / self.width)
+        self.inv_freq = torch.from_numpy(f.astype(np.float32)).to(self.device)
+
+    def on_embedding(self, residual, step):
+        ops.add_sinusoid_(residual, step.positions, self.inv_freq)
+
+
+@FEED_FORWARDS.register("gated_dense")
+class GatedDense(FeedForward):
+    """down(act(gate(x)) * up(x)) with a bias on each of the three products (optional as a set) and ``act`` one of
+    ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) and ``silu``.  gate and up are one matrix, all gate
+    rows first."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.inter = int(params["intermediate_size"])
+        self.act = str(params.get("activation", "gelu_tanh"))
+        self.bias = bool(params.get("bias", True))
+        self.names = params.get("names", ("gate", "up", "down"))
+        self.bias_suffix = params.get("bias_suffix", "b")
+        if self.act not in ops.ACTIVATIONS:
+            raise ValueError(f"gated_dense: activation {self.act!r}; known: {sorted(ops.ACTIVATIONS)}")
+        self.gate_up = None
+        self.down = None
+
+    def tensor_specs(self):
+        g, u, d = self.names
+        specs = [TensorSpec(g, (self.inter, self.hidden)), TensorSpec(u, (self.inter, self.hidden)),
+                 TensorSpec(d, (self.hidden, self.inter))]
+        if self.bias:
+            b = self.bias_suffix
+            specs += [TensorSpec(f"{g}.{b}", (self.inter,), role="bias"), TensorSpec(f"{u}.{b}", (self.inter,), role="bias"),
+                      TensorSpec(f"{d}.{b}", (self.hidden,), role="bias")]
+        return specs
+
+    def bind(self, fetch):
+        g, u, d = self.names
+        b = self.bias_suffix
+        gu_b = self._f32(torch.cat([fetch(f"{g}.{b}").float(), fetch(f"{u}.{b}").float()])) if self.bias else None
+        self.gate_up = Linear(self._matrix(torch.cat([fetch(g), fetch(u)], dim=0)), gu_b)
+        self.down = Linear(self._matrix(fetch(d)), self._f32(fetch(f"{d}.{b}")) if self.bias else None)
+
+    accepts_residual = True
+
+    def forward(self, x, step, residual=None):
+        gu = self.gate_up(x, self.dtype)                                     # [T, 2I], biases added by the product
+        act = ops.act_mul(gu, self.inter, self.dtype, self.act)             # [T, I]
+        return self.down.into(act, residual)
+
+    def weight_bytes(self):
+        return self.gate_up.nbytes() + self.down.nbytes()
+
+
+@BLOCKS.register("parallel_shift")
+class ParallelShiftBlock:
+    """x <- x + (mixer(shift(h)) + ffn(h)) with h = norm(x): one norm, both sublayers read its output.
+
+    The token shift (present when the layer has a ``shift`` tensor role): the mixer reads h + (h' - h) * mix, element
+    by element, with h' the previous token's h as the norm gave it (zeros before a sequence's first token).  The
+    previous h is per-request state of the layer (a `SlotState` named ``shift`` beside whatever the mixer keeps),
+    held in float32.  The feed-forward is optional.
+
+    A term that a product could not add into the stream itself is handed on for the next norm's kernel to add:
+    both of them when that norm is a `GroupRMSNorm` (whose kernel takes two), else one, the other being added
+    here."""
+
+    ROLES = ("norm", "mixer", "ffn", "shift")
+
+    def __init__(self, parts: dict):
+        unknown = set(parts) - set(self.ROLES)
+        if unknown or "norm" not in parts or "mixer" not in parts:
+            raise ValueError(f"the parallel block arranges norm, mixer and optionally ffn and shift; the layer names {sorted(parts)}")
+        self.norm, self.mixer = parts["norm"], parts["mixer"]
+        self.ffn, self.shift = parts.get("ffn"), parts.get("shift")
+        if not isinstance(self.norm, GroupRMSNorm):
+            raise ValueError("the parallel block's norm is a group_rmsnorm (groups=1 for the ordinary one)")
+
+    def cache_need(self):
+        needs = flatten_needs(self.mixer.cache_need())
+        if self.shift is not None:
+            needs.append(SlotState((self.norm.size,), "shift"))
+        return tuple(needs) if needs else None
+
+    accepts_next_norm = True
+
+    @property
+    def first_norm(self):
+        return self.norm
+
+    def forward(self, residual, delta, step, cache, position, write_cache=True, next_norm=None):
+        norm = self.norm
+        rinv = norm.sum_squares(residual, pending_terms(delta))
+        if self.shift is not None:
+            h, hs = ops.group_norm_shift(residual, rinv, norm.weight, norm.dtype, mix=self.shift.mix,
+                                         state=cache.states["shift"], step=step, want_plain=self.ffn is not None)
+        else:
+            h = hs = ops.group_norm_shift(residual, rinv, norm.weight, norm.dtype)
+        kw = {"residual": residual} if getattr(self.mixer, "accepts_residual", False) else {}
+        terms = [self.mixer.forward(hs, step, cache, position, write_cache, **kw)]
+        if self.ffn is not None:
+            kw = {"residual": residual} if getattr(self.ffn, "accepts_residual", False) else {}
+            terms.append(self.ffn.forward(h, step, **kw))
+        terms = [t for t in terms if t is not None]
+        if not terms:
+            return None
+        if len(terms) == 2 and not isinstance(next_norm, GroupRMSNorm):
+            ops.add_group_ssq(residual, terms[:1], 1, 0.0, want_rinv=False)
+            terms = terms[1:]
+        return terms[0] if len(terms) == 1 else tuple(terms)
+
+
+@SHIFTS.register("token_shift")
+class TokenShiftMix(Part):
+    """The per-channel blend of a token shift, h + (h_prev - h) * mix: one float32 vector, the tensor that carries
+    the part's own name, applied inside the norm's kernel."""
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.size = int(params["size"])
+        self.mix = None
+
+    def tensor_specs(self):
+        return [TensorSpec("", (self.size,), role="mix")]
+
+    def bind(self, fetch):
+        self.mix = self._f32(fetch(""))
+
+    def weight_bytes(self):
+        return self.size * 4

@@ -86,7 +86,7 @@ def check(source: TensorSource, specs: Iterable[TensorSpec], *, ignore: Iterable
     missing = [s.name for s in specs if not s.optional and s.name not in have]
     unexpected = sorted(have - set(want) - set(ignore))
     wrong = [(n, want[n].shape, source.shape_of(n)) for n in want
-             if n in have and tuple(source.shape_of(n)) != tuple(want[n].shape)]
+             if n in have and not want[n].fits(source.shape_of(n))]
     other = []
     # optional tensors that belong together must come together
     groups: dict[str, list[TensorSpec]] = {}

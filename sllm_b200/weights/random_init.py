@@ -32,12 +32,15 @@ def random_tensors(specs, seed: int, *, std: float = 0.02, bias_std: float | Non
     for s in specs:
         if s.optional and not include_optional:
             continue
+        shape = s.concrete_shape()
         if s.role == "gain":
-            a = 1.0 + gain_std * rng.standard_normal(s.shape, dtype=np.float32) if gain_std else np.ones(s.shape, np.float32)
+            a = 1.0 + gain_std * rng.standard_normal(shape, dtype=np.float32) if gain_std else np.ones(shape, np.float32)
         elif s.role == "bias":
-            a = bias_std * rng.standard_normal(s.shape, dtype=np.float32)
+            a = bias_std * rng.standard_normal(shape, dtype=np.float32)
+        elif s.role == "mix":              # a blend between two vectors, per channel: values in (0, 1)
+            a = rng.uniform(0.05, 0.95, shape).astype(np.float32)
         else:
-            a = std * rng.standard_normal(s.shape, dtype=np.float32)
+            a = std * rng.standard_normal(shape, dtype=np.float32)
         out[s.name] = torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dt)
     return out
 

@@ -13,8 +13,107 @@ from __future__ import annotations
 import torch
 
 
-def embed_gather(table, ids):
-    return table[ids.long()].float()
+def embed_gather(table, ids, scale=1.0):
+    return table[ids.long()].float() * scale
+
+
+def add_sinusoid_(stream, positions, inv_freq):
+    ang = positions.float()[:, None] * inv_freq[None, :]
+    stream[:, 0::2] += torch.sin(ang)
+    stream[:, 1::2] += torch.cos(ang)
+    return stream
+
+
+def add_group_ssq(stream, terms, groups, eps, want_rinv=True):
+    for t in (terms or ()):
+        if t is not None:
+            stream += t.float().sum(0) if t.dim() == 3 else t.float()
+    if not want_rinv:
+        return None
+    T, W = stream.shape
+    return (stream.reshape(T, groups, W // groups).pow(2).mean(-1) + eps).rsqrt()
+
+
+def group_norm_shift(stream, rinv, gain, out_dtype, *, mix=None, state=None, step=None, want_plain=True):
+    T, W = stream.shape
+    groups = rinv.shape[1]
+    h = (stream.reshape(T, groups, W // groups) * rinv[:, :, None]).reshape(T, W) * gain
+    if mix is None:
+        return h.to(out_dtype)
+    prev = torch.empty_like(h)
+    prev[1:] = h[:-1]
+    starts = step.q_start.long().tolist()
+    for s in range(step.num_seqs):
+        slot = int(step.state_slots[s])
+        prev[starts[s]] = state[slot]
+        state[slot] = h[starts[s + 1] - 1]
+    hs = h + (prev - h) * mix
+    return (h.to(out_dtype) if want_plain else None), hs.to(out_dtype)
+
+
+def act_mul(gu, interleave, out_dtype, act):
+    T, two_i = gu.shape
+    I = two_i // 2
+    v = gu.float().reshape(T, I // interleave, 2, interleave)
+    g, u = v[:, :, 0, :], v[:, :, 1, :]
+    if act == "silu":
+        a = g / (1.0 + torch.exp(-g))
+    else:
+        a = 0.5 * g * (1.0 + torch.tanh(0.7978845608028654 * (g + 0.044715 * g ** 3)))
+    return (a * u).reshape(T, I).to(out_dtype)
+
+
+def tanh_cols(x, col0, n, out_dtype):
+    return torch.tanh(x[:, col0:col0 + n]).to(out_dtype)
+
+
+def delta_rule(proj, offs, decay, a_bias, state, step, heads, dk, dv):
+    T = proj.shape[0]
+    off_r, off_k, off_v, off_a = offs
+    C = heads * dk
+    r = proj[:, off_r:off_r + C].reshape(T, heads, dk)
+    k = proj[:, off_k:off_k + C].reshape(T, heads, dk)
+    v = proj[:, off_v:off_v + heads * dv].reshape(T, heads, dv)
+    a = torch.sigmoid(proj[:, off_a:off_a + C] + a_bias).reshape(T, heads, dk)
+    d = torch.exp(-float(torch.exp(torch.tensor(-0.5))) * torch.sigmoid(decay)).reshape(T, heads, dk)
+    u = k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)
+    out = torch.empty((T, heads, dv), dtype=torch.float32, device=proj.device)
+    starts = step.q_start.long().tolist()
+    for s in range(step.num_seqs):
+        slot = int(step.state_slots[s])
+        S = state[slot].clone()
+        for t in range(starts[s], starts[s + 1]):
+            uS = torch.einsum("hi,hij->hj", u[t], S)
+            S = d[t][:, :, None] * S - (a[t] * u[t])[:, :, None] * uS[:, None, :] + k[t][:, :, None] * v[t][:, None, :]
+            out[t] = torch.einsum("hij,hi->hj", S, r[t])
+        state[slot] = S
+    return out.reshape(T, heads * dv)
+
+
+def delta_out(o, gain, proj, off_g, eps, heads, dv, out_dtype):
+    T = o.shape[0]
+    x = o.reshape(T, heads, dv)
+    x = x * (x.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
+    return (x.reshape(T, heads * dv) * gain * torch.sigmoid(proj[:, off_g:off_g + heads * dv])).to(out_dtype)
+
+
+def latent_write(proj, off, rank, gain, eps, slot_mapping, cache):
+    x = proj[:, off:off + rank]
+    c = x * (x.pow(2).mean(-1, keepdim=True) + eps).rsqrt() * gain
+    ps = cache.shape[2]
+    ok = slot_mapping >= 0
+    slots = slot_mapping[ok].long()
+    cache[slots // ps, 0, slots % ps, :] = c[ok].to(cache.dtype)
+
+
+def head_linear(x, xoff, w, out_dtype, *, gate=None, goff=0):
+    H, dout, din = w.shape
+    T = x.shape[0]
+    xs = x[:, xoff:xoff + H * din].float().reshape(T, H, din)
+    out = torch.einsum("thi,hoi->tho", xs, w.float())
+    if gate is not None:
+        out = out * torch.sigmoid(gate[:, goff:goff + H])[:, :, None]
+    return out.reshape(T, H * dout).to(out_dtype)
 
 
 def add_rmsnorm(residual, delta, weight, eps, out_dtype):
@@ -152,5 +251,6 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
+ALL = ["add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
+       "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
        "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_", "mark_seen", "penalty_from_seen_"]
