@@ -24,7 +24,7 @@ from ..config.registry import Architecture, register_architecture
 
 NAME = "Rososun"
 MIXER_TYPES = ("general_delta", "latent_attention")
-MAX_POSITIONS = 1 << 20      # the design has no limit; float32 positions and angles are exact far beyond this
+MAX_POSITIONS = 1 << 17      # the design itself has no limit; this is the engine's (a request's block table is sized for it)
 
 
 def _section(raw: dict, key: str) -> dict:
@@ -140,4 +140,13 @@ def plan(cfg: RososunConfig) -> ModelPlan:
     return p
 
 
-register_architecture(Architecture(name=NAME, config_cls=RososunConfig, plan=plan, aliases=("rososun",)), replace=True)
+def config_from_recipe(t: dict) -> dict:
+    """A recipe's inline geometry carries config.json's own keys (``vocab``, ``width``, ``embedding``, ``norm``,
+    ``layers``); a missing one raises KeyError naming it."""
+    cfg = {k: t[k] for k in ("vocab", "width", "embedding", "norm", "layers")}
+    cfg["architecture"] = NAME
+    return cfg
+
+
+register_architecture(Architecture(name=NAME, config_cls=RososunConfig, plan=plan, aliases=("rososun",),
+                                   config_from_recipe=config_from_recipe), replace=True)
