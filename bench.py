@@ -216,7 +216,8 @@ def decode_run(model, cfg, batch, context, steps, warmup, seed=0, graphs=True, r
     mid = sorted(range(repeats), key=lambda r: dev[r])[repeats // 2]
     ctx_mean = prompt_len + warmup + mid * steps + (steps - 1) / 2.0
     kv_bytes = llm.engine.cache.bytes_per_token(2 if model.dtype == torch.bfloat16 else 4) * ctx_mean * batch
-    step_bytes = model.weight_bytes() + kv_bytes
+    # (a recurrent layer's state is read and written once a step and request; none in an attention-only model)
+    step_bytes = model.weight_bytes() + kv_bytes + 2 * llm.engine.cache.state_bytes_per_request() * batch
     # per step: the packed batch description (one pinned buffer: ids, positions, slots, block tables, sampling
     # inputs) goes up, the sampled ids come down; counted from the tensors the engine copied
     # (per step the device ran: with a step queued ahead, the window may hold one launch more or less)
@@ -376,6 +377,67 @@ def serving_run(which: str, layers: int | None = None) -> dict:
                    "kv_dtype": "bf16", "parallelism": "1 GPU"},
         "gpu_launches": r["own"], "library_launches": r["library"], "clocks": r["clocks"],
     }
+
+
+# ---- another design beside the closest existing one, at equal sizes ---------------------------------------------------
+# (--workload rososun) Layer sizes that resemble a real model's; random weights; prefill of one prompt and decode steps
+# of a batch, each design through the same engine, with the device time of every kernel entry point.
+
+DESIGN_SIZES = {
+    # name: width, layers, heads x dim of attention, feed-forward size, vocabulary, latent size
+    "w2048": dict(width=2048, layers=8, heads=16, dim=128, ff=5632, vocab=32000, kv_rank=128),
+    "w4096": dict(width=4096, layers=4, heads=32, dim=128, ff=11008, vocab=32000, kv_rank=128),
+}
+
+
+def design_configs(sz: dict):
+    """(Rososun config, Qwen2 config) of one size: the same width, depth, feed-forward and vocabulary; Rososun's layers
+    alternate between its two mixers (recurrent heads of 64 channels, latent attention over one latent vector per token),
+    Qwen2 has grouped-query attention with an eighth of the heads as kv heads."""
+    W, H, D = sz["width"], sz["heads"], sz["dim"]
+    delta = {"type": "general_delta", "mixer": {"heads": W // 64, "dim": 64, "decay_rank": 64}, "mlp": {"kind": "dense", "ff": sz["ff"]}}
+    latent = {"type": "latent_attention", "mixer": {"heads": H, "dim": D, "vdim": D, "kv_rank": sz["kv_rank"], "scale": D ** -0.5},
+              "mlp": {"kind": "dense", "ff": sz["ff"]}}
+    ours = {"architecture": "Rososun", "vocab": sz["vocab"], "width": W, "embedding": {"scale": 1.0}, "norm": {"eps": 1e-5, "groups": 4},
+            "layers": [delta if i % 2 == 0 else latent for i in range(sz["layers"])]}
+    qwen = {"architectures": ["Qwen2ForCausalLM"], "model_type": "qwen2", "num_hidden_layers": sz["layers"], "hidden_size": W,
+            "num_attention_heads": H, "num_key_value_heads": max(1, H // 8), "head_dim": D, "intermediate_size": sz["ff"],
+            "vocab_size": sz["vocab"], "rope_theta": 10000.0, "rms_norm_eps": 1e-5, "max_position_embeddings": 8192,
+            "tie_word_embeddings": False, "hidden_act": "silu"}
+    return ours, qwen
+
+
+def design_run(args) -> dict:
+    global PREFILL_TOKENS
+    import torch
+
+    from sllm_b200.engine import build_random_model
+    peaks, peaks_kind = load_peaks()
+    out = {"workload": "rososun", "dtype": "bfloat16", "data": "synthetic (random weights, uniform random token ids)",
+           "prefill_tokens": args.prefill_tokens, "decode": {"batch": args.batch, "context": args.context},
+           "peaks": dict(peaks, kind=peaks_kind), "sizes": {}}
+    for name, sz in DESIGN_SIZES.items():
+        rec = {}
+        for which, config in zip(("rososun", "qwen2"), design_configs(sz)):
+            model, _ = build_random_model(config, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
+            cfg = {"vocab_size": sz["vocab"]}
+            torch.cuda.synchronize()
+            ms = prefill_run(model, cfg, args.prefill_tokens)
+            dec = decode_run(model, cfg, args.batch, args.context, args.steps, max(3, args.warmup), repeats=3)
+            keep, PREFILL_TOKENS = PREFILL_TOKENS, args.prefill_tokens
+            try:
+                kt = kernel_times(model, cfg, args.batch, min(args.context, 1024))
+            finally:
+                PREFILL_TOKENS = keep
+            rec[which] = {"prefill_ms": round(ms, 3), "prefill_tok_s": round(args.prefill_tokens / (ms / 1e3)),
+                          "decode_ms_per_step": round(dec["ms_per_step"], 4), "decode_tok_s": round(dec["tok_s"]),
+                          "decode_step_bytes": int(dec["step_bytes"]),
+                          "decode_hbm_frac": round(dec["step_bytes"] / (dec["ms_per_step"] / 1e3) / (peaks["hbm_gbs"] * 1e9), 3),
+                          "weight_bytes": int(model.weight_bytes()), "clocks": dec["clocks"], "kernel_ms": kt}
+            del model
+            torch.cuda.empty_cache()
+        out["sizes"][name] = dict(sz, **rec)
+    return out
 
 
 def logit_check(cfg, tokens=64, layers=2, seed=11):
@@ -630,7 +692,7 @@ def base_config(cfg, args, prompt_len) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=("decode",) + tuple(SERVING), default="decode",
+    ap.add_argument("--workload", choices=("decode", "rososun") + tuple(SERVING), default="decode",
                     help="decode: the default run; serve-*: the baseline's serving workloads through LLM.generate")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -669,6 +731,9 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
+    if args.workload == "rososun":
+        print(json.dumps(design_run(args)))
+        return 0
     if args.workload != "decode":
         print(json.dumps(serving_run(args.workload, args.layers)))
         return 0

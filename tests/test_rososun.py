@@ -74,8 +74,21 @@ def plain_logits(d, reqs):
     return {r: plain.forward(ids, cfg, w).astype(np.float32) for r, ids in reqs.items()}
 
 
-def tolerance(dtype):
-    return dict(rtol=2e-4, atol=2e-4) if dtype == "float32" else dict(rtol=6e-2, atol=6e-2)
+def compare(tr, out, want, dtype, what):
+    """float32: every logit to 2e-4.  bfloat16: the difference of a row (mean taken off, root mean square over the
+    vocabulary) relative to the row's own spread is rounding's: under 2 % for 19 rows in 20 and under 8 % for every row
+    (measured: median 0.4 %, the worst row 3.4 %; a lost key or state moves rows by tens of per cent)."""
+    if dtype == "float32":
+        return traces.compare(tr, out, want, what=what, rtol=2e-4, atol=2e-4)
+    errs = []
+    for s in tr.steps:
+        for row, (req, pos) in enumerate(s["expect"]):
+            ref, got = want[req][pos], out[s["step"]][row]
+            d, r = got - ref, ref - ref.mean()
+            e = float(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((r ** 2).mean()))
+            assert e < 0.08, f"{what}: step {s['step']}, request {req!r}, position {pos}: relative difference {e:.3g}"
+            errs.append(e)
+    assert np.quantile(errs, 0.95) < 0.02, f"{what}: 95th percentile of the rows' relative difference {np.quantile(errs, 0.95):.3g}"
 
 
 def dtypes_on(dev):
@@ -282,7 +295,7 @@ def test_every_cutting_against_plain(tmp_path, dev, which):
             tr = getattr(traces, mode)(reqs)
             eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=4, poison_freed=True)
             out = traces.replay_engine(tr, eng)
-            traces.compare(tr, out, want, what=f"{which}/{dtype}/{mode}", **tolerance(dtype))
+            compare(tr, out, want, dtype, f"{which}/{dtype}/{mode}")
             eng.cache.check()
             assert not eng.cache.requests and all(g.pool.used_count == 0 for g in eng.cache.groups)
             if mode == "mixed":
@@ -349,7 +362,7 @@ def test_keys_far_back_at_page_borders_and_a_long_memory(tmp_path, dev):
             at += 1
         eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=1, poison_freed=True)
         out = traces.replay_engine(tr, eng)
-        traces.compare(tr, out, want, what=f"far/{dtype}", **tolerance(dtype))
+        compare(tr, out, want, dtype, f"far/{dtype}")
 
 
 def test_greedy_generation_through_the_entry_point(tmp_path, dev):
@@ -416,4 +429,4 @@ def test_replay_program_on_a_model_folder(tmp_path):
     for dtype in ("float32", "bfloat16"):
         out_dir = os.path.join(str(tmp_path), f"out_{dtype}")
         out = traces.replay_subprocess(tr, d, dtype, out_dir, 16)
-        traces.compare(tr, out, want, what=f"replay/{dtype}", **tolerance(dtype))
+        compare(tr, out, want, dtype, f"replay/{dtype}")
