@@ -9,11 +9,14 @@
 // outputs are float32.
 //
 // The columns of S evolve independently of one another (column j needs u, d, a*u, k, r of the token and
-// v_j only), so a CTA owns a slice of DR_COLS columns of one (request, head) and walks the request's tokens
-// in order.  Four consecutive lanes share a column, each holding every fourth row in registers; the two
-// sums over rows of a step are two shuffles each.  The token's vectors are prepared for DR_CHUNK tokens at a
-// time in shared memory (one CTA-wide barrier pair per chunk, none per token).  A portion of a prompt and
-// a single decoded token run through the same kernel, from the state slot and back into it.
+// v_j only), so a CTA owns a slice of 64 columns of one (request, head) and walks the request's tokens in
+// order.  Eight consecutive lanes share four columns, each lane holding every eighth row of them in registers
+// (a token's five vectors are read from shared memory once per four columns); the two sums over rows of a
+// step end in shuffles among the eight.  Four warps compute; four more prepare the next chunk of tokens in the
+// other half of shared memory meanwhile (unit keys, decays, rates: a warp per token, all of a token's loads in
+// flight at once), so the walk never waits for global memory: one CTA-wide barrier per chunk, none per token.
+// A portion of a prompt and a single decoded token run through the same kernel, from the state slot and back
+// into it.
 //
 // A second kernel finishes the mixer's output: each head's o over its root mean square, times a gain,
 // times sigmoid(gate logit), in the compute dtype.
@@ -21,9 +24,8 @@
 
 namespace sllm {
 
-constexpr int DR_COLS = 32;      // columns of S per CTA
-constexpr int DR_SPLIT = 4;      // lanes per column
-constexpr int DR_THREADS = DR_COLS * DR_SPLIT;
+constexpr int DR_COMPUTE = 128;   // threads that walk the tokens (as many again prepare the next chunk)
+constexpr int DR_THREADS = 2 * DR_COMPUTE;
 constexpr int DR_MAX_CHUNK = 16;
 
 __device__ __forceinline__ float sigmoidf_(float z) { return 1.0f / (1.0f + expf(-z)); }
@@ -39,96 +41,150 @@ struct DeltaParams {
   int ld, off_r, off_k, off_v, off_a, H, dk, dv, chunk;
 };
 
-// RPT: rows of a column per lane (dk <= 4 * RPT).
+// RPT: rows of a column per lane (dk <= 8 * RPT = DKP, the padded key size).
+constexpr int DR_SPLIT = 8, DR_CB = 4, DR_COLS = DR_COMPUTE / DR_SPLIT * DR_CB;      // 64 columns a CTA
+
 template <int RPT>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParams p) {
-  extern __shared__ float sm[];
+  constexpr int SPLIT = DR_SPLIT, CB = DR_CB, COLS = DR_COLS, DKP = RPT * SPLIT, PER_LANE = (DKP + 31) / 32;
+  extern __shared__ __align__(16) float sm[];
   const int dk = p.dk, dv = p.dv, chunk = p.chunk;
-  float* s_u = sm;                        // [chunk][dk] unit key
-  float* s_d = s_u + chunk * dk;          // decay
-  float* s_au = s_d + chunk * dk;         // removal rate * unit key
-  float* s_k = s_au + chunk * dk;
-  float* s_r = s_k + chunk * dk;
-  float* s_v = s_r + chunk * dk;          // [chunk][DR_COLS]
-  float* s_ss = s_v + chunk * DR_COLS;    // [chunk] sum of k^2
+  const int buf_floats = chunk * (5 * DKP + COLS);
   pdl_wait();
-  const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * DR_COLS;
+  const int seq = blockIdx.x, h = blockIdx.y, c0 = blockIdx.z * COLS;
   const int t_begin = p.q_start[seq], t_end = p.q_start[seq + 1];
-  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
-  const int col = c0 + tid / DR_SPLIT, rs = tid % DR_SPLIT;
-  const bool live = col < dv;
-  float* S = p.state + ((size_t)p.state_slots[seq] * p.H + h) * dk * dv;
-  float s[RPT];
-#pragma unroll
-  for (int n = 0; n < RPT; ++n) {
-    const int i = n * DR_SPLIT + rs;
-    s[n] = (live && i < dk) ? S[(size_t)i * dv + col] : 0.f;
-  }
-  const float c_decay = -expf(-0.5f);
-  for (int t0 = t_begin; t0 < t_end; t0 += chunk) {
-    const int nt = min(chunk, t_end - t0);
-    __syncthreads();                       // the chunk before has been read
-    // sum of squares of each token's key: a warp per token
-    for (int tt = warp; tt < nt; tt += DR_THREADS / 32) {
-      const float* k = p.proj + (size_t)(t0 + tt) * p.ld + p.off_k + h * dk;
-      float ss = 0.f;
-      for (int i = lane; i < dk; i += 32) ss = fmaf(k[i], k[i], ss);
-      ss = warp_sum(ss);
-      if (lane == 0) s_ss[tt] = ss;
-    }
-    __syncthreads();
-    for (int e = tid; e < nt * dk; e += DR_THREADS) {
-      const int tt = e / dk, i = e % dk;
+  const int tid = threadIdx.x, lane = tid & 31;
+  const bool loader = tid >= DR_COMPUTE;
+  const int nchunks = (t_end - t_begin + chunk - 1) / chunk;
+
+  // a loader warp prepares token after token of chunk c: rows of u, d, a*u, k, r (zeros beyond dk) and v's slice
+  auto prepare = [&](int c) {
+    float* b = sm + (c & 1) * buf_floats;
+    float* s_u = b, *s_d = b + chunk * DKP, *s_au = b + 2 * chunk * DKP, *s_k = b + 3 * chunk * DKP, *s_r = b + 4 * chunk * DKP;
+    float* s_v = b + 5 * chunk * DKP;
+    const int t0 = t_begin + c * chunk, nt = min(chunk, t_end - t0);
+    const float c_decay = -expf(-0.5f);
+    for (int tt = (tid - DR_COMPUTE) >> 5; tt < nt; tt += DR_COMPUTE / 32) {
       const float* row = p.proj + (size_t)(t0 + tt) * p.ld;
-      const float k = row[p.off_k + h * dk + i];
-      const float u = k / sqrtf(s_ss[tt] + 1e-6f);
-      const float a = sigmoidf_(row[p.off_a + h * dk + i] + p.a_bias[h * dk + i]);
-      s_k[e] = k;
-      s_u[e] = u;
-      s_au[e] = a * u;
-      s_d[e] = expf(c_decay * sigmoidf_(p.decay[(size_t)(t0 + tt) * p.H * dk + h * dk + i]));
-      s_r[e] = row[p.off_r + h * dk + i];
-    }
-    for (int e = tid; e < nt * DR_COLS; e += DR_THREADS) {
-      const int tt = e / DR_COLS, j = c0 + e % DR_COLS;
-      s_v[e] = j < dv ? p.proj[(size_t)(t0 + tt) * p.ld + p.off_v + h * dv + j] : 0.f;
-    }
-    __syncthreads();
-    for (int tt = 0; tt < nt; ++tt) {
-      const float* u = s_u + tt * dk;
-      const float* d = s_d + tt * dk;
-      const float* au = s_au + tt * dk;
-      const float* k = s_k + tt * dk;
-      const float* r = s_r + tt * dk;
-      float us = 0.f;
+      const float* dec = p.decay + (size_t)(t0 + tt) * p.H * dk + h * dk;
+      float k[PER_LANE], a[PER_LANE], d[PER_LANE], r[PER_LANE], v[COLS / 32];
+      float ss = 0.f;
 #pragma unroll
-      for (int n = 0; n < RPT; ++n) {
-        const int i = n * DR_SPLIT + rs;
-        if (i < dk) us = fmaf(u[i], s[n], us);
+      for (int m = 0; m < PER_LANE; ++m) {
+        const int i = lane + 32 * m;
+        const bool in = i < dk;
+        k[m] = in ? __ldg(row + p.off_k + h * dk + i) : 0.f;
+        a[m] = in ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
+        d[m] = in ? __ldg(dec + i) : 0.f;
+        r[m] = in ? __ldg(row + p.off_r + h * dk + i) : 0.f;
       }
-      us += __shfl_xor_sync(0xffffffffu, us, 1);
-      us += __shfl_xor_sync(0xffffffffu, us, 2);
-      const float v = s_v[tt * DR_COLS + tid / DR_SPLIT];
-      float o = 0.f;
 #pragma unroll
-      for (int n = 0; n < RPT; ++n) {
-        const int i = n * DR_SPLIT + rs;
-        if (i < dk) {
-          s[n] = fmaf(k[i], v, fmaf(-au[i], us, d[i] * s[n]));
-          o = fmaf(s[n], r[i], o);
+      for (int m = 0; m < COLS / 32; ++m) {
+        const int j = c0 + lane + 32 * m;
+        v[m] = j < dv ? __ldg(row + p.off_v + h * dv + j) : 0.f;
+      }
+#pragma unroll
+      for (int m = 0; m < PER_LANE; ++m) ss = fmaf(k[m], k[m], ss);
+      ss = warp_sum(ss);
+      const float inv = 1.0f / sqrtf(ss + 1e-6f);
+#pragma unroll
+      for (int m = 0; m < PER_LANE; ++m) {
+        const int i = lane + 32 * m;
+        if (i < DKP) {
+          const bool in = i < dk;
+          const float u = k[m] * inv;
+          s_k[tt * DKP + i] = k[m];
+          s_u[tt * DKP + i] = u;
+          s_au[tt * DKP + i] = in ? sigmoidf_(a[m]) * u : 0.f;
+          s_d[tt * DKP + i] = in ? expf(c_decay * sigmoidf_(d[m])) : 0.f;
+          s_r[tt * DKP + i] = r[m];
         }
       }
-      o += __shfl_xor_sync(0xffffffffu, o, 1);
-      o += __shfl_xor_sync(0xffffffffu, o, 2);
-      if (live && rs == 0) p.out[(size_t)(t0 + tt) * p.H * dv + h * dv + col] = o;
+#pragma unroll
+      for (int m = 0; m < COLS / 32; ++m) s_v[tt * COLS + lane + 32 * m] = v[m];
     }
-  }
-  pdl_launch_dependents();
-  if (live) {
+  };
+
+  const int cg = (tid % DR_COMPUTE) / SPLIT, rs = tid % SPLIT;     // this lane's four columns c0 + 4 cg .., its rows rs + 8 n
+  const int col = c0 + cg * CB;
+  float* S = p.state + ((size_t)p.state_slots[seq] * p.H + h) * dk * dv;
+  float s[RPT][CB];
+  if (loader) {
+    if (nchunks > 0) prepare(0);
+  } else {
 #pragma unroll
     for (int n = 0; n < RPT; ++n) {
-      const int i = n * DR_SPLIT + rs;
-      if (i < dk) S[(size_t)i * dv + col] = s[n];
+      const int i = n * SPLIT + rs;
+#pragma unroll
+      for (int c = 0; c < CB; ++c) s[n][c] = (i < dk && col + c < dv) ? S[(size_t)i * dv + col + c] : 0.f;
+    }
+  }
+  __syncthreads();
+  for (int c = 0; c < nchunks; ++c) {
+    if (loader) {
+      if (c + 1 < nchunks) prepare(c + 1);
+    } else {
+      const float* b = sm + (c & 1) * buf_floats;
+      const int t0 = t_begin + c * chunk, nt = min(chunk, t_end - t0);
+#pragma unroll 2
+      for (int tt = 0; tt < nt; ++tt) {
+        const float* u = b + tt * DKP + rs;
+        const float* d = u + chunk * DKP;
+        const float* au = d + chunk * DKP;
+        const float* k = au + chunk * DKP;
+        const float* r = k + chunk * DKP;
+        const float4 v = *reinterpret_cast<const float4*>(b + 5 * chunk * DKP + tt * COLS + cg * CB);
+        float us[CB] = {0.f, 0.f, 0.f, 0.f}, ut[CB] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < RPT; n += 2) {
+          const float ua = u[n * SPLIT], ub = u[(n + 1) * SPLIT];
+#pragma unroll
+          for (int cc = 0; cc < CB; ++cc) {
+            us[cc] = fmaf(ua, s[n][cc], us[cc]);
+            ut[cc] = fmaf(ub, s[n + 1][cc], ut[cc]);
+          }
+        }
+#pragma unroll
+        for (int cc = 0; cc < CB; ++cc) {
+          us[cc] += ut[cc];
+#pragma unroll
+          for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
+        }
+        const float vv[CB] = {v.x, v.y, v.z, v.w};
+        float o[CB] = {0.f, 0.f, 0.f, 0.f}, o2[CB] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+        for (int n = 0; n < RPT; n += 2) {
+          const float ka = k[n * SPLIT], kb = k[(n + 1) * SPLIT], aa = -au[n * SPLIT], ab = -au[(n + 1) * SPLIT];
+          const float da = d[n * SPLIT], db = d[(n + 1) * SPLIT], ra = r[n * SPLIT], rb = r[(n + 1) * SPLIT];
+#pragma unroll
+          for (int cc = 0; cc < CB; ++cc) {
+            s[n][cc] = fmaf(ka, vv[cc], fmaf(aa, us[cc], da * s[n][cc]));
+            s[n + 1][cc] = fmaf(kb, vv[cc], fmaf(ab, us[cc], db * s[n + 1][cc]));
+            o[cc] = fmaf(s[n][cc], ra, o[cc]);
+            o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
+          }
+        }
+        // the four sums over eight lanes in four shuffles: halves of the values change hands, then quarters; lane rs
+        // ends with the whole sum of column 2 (rs & 1) + ((rs >> 1) & 1)
+        const bool odd = rs & 1, hi = rs & 2;
+        float a0 = (odd ? o[2] + o2[2] : o[0] + o2[0]) + __shfl_xor_sync(0xffffffffu, odd ? o[0] + o2[0] : o[2] + o2[2], 1);
+        float a1 = (odd ? o[3] + o2[3] : o[1] + o2[1]) + __shfl_xor_sync(0xffffffffu, odd ? o[1] + o2[1] : o[3] + o2[3], 1);
+        float tot = (hi ? a1 : a0) + __shfl_xor_sync(0xffffffffu, hi ? a0 : a1, 2);
+        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+        const int mine = col + 2 * (rs & 1) + ((rs >> 1) & 1);
+        if (rs < 4 && mine < dv) p.out[(size_t)(t0 + tt) * p.H * dv + h * dv + mine] = tot;
+      }
+    }
+    __syncthreads();
+  }
+  pdl_launch_dependents();
+  if (!loader) {
+#pragma unroll
+    for (int n = 0; n < RPT; ++n) {
+      const int i = n * SPLIT + rs;
+#pragma unroll
+      for (int cc = 0; cc < CB; ++cc)
+        if (i < dk && col + cc < dv) S[(size_t)i * dv + col + cc] = s[n][cc];
     }
   }
 }
@@ -157,7 +213,29 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
 
 using namespace sllm;
 
-SLLM_EXPORT int sllm_delta_rule_supports(int dk, int dv) { return dk >= 1 && dk <= 256 && dv >= 1 && dv <= 65535 * DR_COLS; }
+SLLM_EXPORT int sllm_delta_rule_supports(int dk, int dv) { return dk >= 1 && dk <= 256 && dv >= 1 && dv <= 65535 * 16; }
+
+template <int RPT>
+static int launch_delta_rule(DeltaParams p, int S, cudaStream_t stream) {
+  constexpr int DKP = RPT * DR_SPLIT;
+  const size_t per_token = (size_t)(5 * DKP + DR_COLS) * sizeof(float);
+  int chunk = (int)((96 * 1024) / (2 * per_token));
+  chunk = chunk > DR_MAX_CHUNK ? DR_MAX_CHUNK : (chunk < 1 ? 1 : chunk);
+  p.chunk = chunk;
+  const size_t smem = 2 * per_token * chunk;
+  static size_t allowed = 48 * 1024;          // (per instantiation: what the kernel has been told it may use)
+  if (smem > allowed) {
+    if (cudaFuncSetAttribute(delta_rule_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+      cudaGetLastError();
+      set_error("delta_rule: the kernel's shared memory could not be raised");
+      return SLLM_ERR_LAUNCH;
+    }
+    allowed = smem;
+  }
+  const dim3 grid((unsigned)S, (unsigned)p.H, (unsigned)((p.dv + DR_COLS - 1) / DR_COLS));
+  launch_kernel(delta_rule_kernel<RPT>, grid, DR_THREADS, smem, stream, p);
+  return launch_status("delta_rule");
+}
 
 SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* decay,
                                 const float* a_bias, float* state, const int* q_start, const int* state_slots, float* out,
@@ -170,18 +248,12 @@ SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k,
   DeltaParams p;
   p.proj = proj; p.decay = decay; p.a_bias = a_bias; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
   p.out = out; p.ld = ld; p.off_r = off_r; p.off_k = off_k; p.off_v = off_v; p.off_a = off_a; p.H = H; p.dk = dk; p.dv = dv;
-  const size_t per_token = (size_t)(5 * dk + DR_COLS + 1) * sizeof(float);
-  int chunk = (int)((44 * 1024) / per_token);
-  chunk = chunk > DR_MAX_CHUNK ? DR_MAX_CHUNK : (chunk < 1 ? 1 : chunk);
-  p.chunk = chunk;
-  const size_t smem = per_token * chunk;
-  const dim3 grid((unsigned)S, (unsigned)H, (unsigned)((dv + DR_COLS - 1) / DR_COLS));
-  if (dk <= 16) launch_kernel(delta_rule_kernel<4>, grid, DR_THREADS, smem, stream, p);
-  else if (dk <= 32) launch_kernel(delta_rule_kernel<8>, grid, DR_THREADS, smem, stream, p);
-  else if (dk <= 64) launch_kernel(delta_rule_kernel<16>, grid, DR_THREADS, smem, stream, p);
-  else if (dk <= 128) launch_kernel(delta_rule_kernel<32>, grid, DR_THREADS, smem, stream, p);
-  else launch_kernel(delta_rule_kernel<64>, grid, DR_THREADS, smem, stream, p);
-  return launch_status("delta_rule");
+  p.chunk = 1;
+  if (dk <= 16) return launch_delta_rule<2>(p, S, stream);
+  if (dk <= 32) return launch_delta_rule<4>(p, S, stream);
+  if (dk <= 64) return launch_delta_rule<8>(p, S, stream);
+  if (dk <= 128) return launch_delta_rule<16>(p, S, stream);
+  return launch_delta_rule<32>(p, S, stream);
 }
 
 SLLM_EXPORT int sllm_delta_out(const float* o, const float* gain, const float* proj, int ld, int off_g, float eps, void* out,

@@ -7,8 +7,10 @@
 //     head's query into the latent space (W_h = the head's key up-projection, transposed: the score of a
 //     query against a key is then its carried form against the cached latent) and the head's weighted sum
 //     of latents back out through the value up-projection; there the result can be multiplied by
-//     sigmoid(gate[t, h]) as it is written.  float32 accumulation over din in a fixed order.
+//     sigmoid(gate[t, h]) as it is written.  float32 accumulation over din in a fixed order: on the CUDA cores
+//     for the float32 path, on the tensor cores (mma.sync) for bfloat16 operands.
 #include "common.cuh"
+#include "mma.cuh"
 
 namespace sllm {
 
@@ -89,6 +91,94 @@ head_linear_kernel(const TX* __restrict__ x, int ldx, int xoff, const TW* __rest
   }
 }
 
+// The same product on the tensor cores (mma.sync m16n8k16, bfloat16 operands, float32 accumulation) for the
+// bfloat16 path: a CTA of four warps makes 64 tokens x 64 outputs of one head, a warp 16 tokens x 64; x (bfloat16, or
+// float32 rounded to bfloat16 as it is staged) and W_h are staged 32 columns of din at a time in shared memory,
+// rows padded to 40 elements so that the fragments' 32-bit reads fall in distinct banks.
+constexpr int HM_BM = 64, HM_BN = 64, HM_BK = 32, HM_LD = HM_BK + 8;
+
+template <typename TX>
+__global__ void __launch_bounds__(128)
+head_linear_mma_kernel(const TX* __restrict__ x, int ldx, int xoff, const __nv_bfloat16* __restrict__ w,
+                       __nv_bfloat16* __restrict__ out, const float* __restrict__ gate, int ldg, int goff, int T, int H,
+                       int din, int dout, int vec) {
+  __shared__ __align__(16) __nv_bfloat16 Xs[HM_BM][HM_LD];
+  __shared__ __align__(16) __nv_bfloat16 Ws[HM_BN][HM_LD];
+  pdl_wait();
+  const int h = blockIdx.z, m0 = blockIdx.y * HM_BM, n0 = blockIdx.x * HM_BN;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5, g = lane >> 2, t4 = lane & 3;
+  const TX* xh = x + xoff + (size_t)h * din;
+  const __nv_bfloat16* wh = w + (size_t)h * dout * din;
+  float acc[8][4];
+#pragma unroll
+  for (int j = 0; j < 8; ++j)
+#pragma unroll
+    for (int c = 0; c < 4; ++c) acc[j][c] = 0.f;
+  for (int k0 = 0; k0 < din; k0 += HM_BK) {
+    __syncthreads();
+    // stage x: 64 rows x 32 columns
+    if (vec) {
+      if constexpr (sizeof(TX) == 2) {
+        for (int c = tid; c < HM_BM * 4; c += 128) {
+          const int r = c >> 2, kc = (c & 3) * 8;
+          uint4 v = make_uint4(0, 0, 0, 0);
+          if (m0 + r < T && k0 + kc < din) v = *reinterpret_cast<const uint4*>(xh + (size_t)(m0 + r) * ldx + k0 + kc);
+          *reinterpret_cast<uint4*>(&Xs[r][kc]) = v;
+        }
+      } else {
+        for (int c = tid; c < HM_BM * 8; c += 128) {
+          const int r = c >> 3, kc = (c & 7) * 4;
+          float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+          if (m0 + r < T && k0 + kc < din) v = *reinterpret_cast<const float4*>(xh + (size_t)(m0 + r) * ldx + k0 + kc);
+          *reinterpret_cast<uint2*>(&Xs[r][kc]) = make_uint2(pack_bf16(v.x, v.y), pack_bf16(v.z, v.w));
+        }
+      }
+      for (int c = tid; c < HM_BN * 4; c += 128) {
+        const int r = c >> 2, kc = (c & 3) * 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (n0 + r < dout && k0 + kc < din) v = *reinterpret_cast<const uint4*>(wh + (size_t)(n0 + r) * din + k0 + kc);
+        *reinterpret_cast<uint4*>(&Ws[r][kc]) = v;
+      }
+    } else {
+      for (int c = tid; c < HM_BM * HM_BK; c += 128) {
+        const int r = c / HM_BK, k = c % HM_BK;
+        Xs[r][k] = (m0 + r < T && k0 + k < din) ? from_f32<__nv_bfloat16>(to_f32(xh[(size_t)(m0 + r) * ldx + k0 + k])) : __float2bfloat16_rn(0.f);
+        Ws[r][k] = (n0 + r < dout && k0 + k < din) ? wh[(size_t)(n0 + r) * din + k0 + k] : __float2bfloat16_rn(0.f);
+      }
+    }
+    __syncthreads();
+#pragma unroll
+    for (int kk = 0; kk < HM_BK; kk += 16) {
+      unsigned a[4];
+      const int r = warp * 16 + g;
+      a[0] = *reinterpret_cast<const unsigned*>(&Xs[r][kk + 2 * t4]);
+      a[1] = *reinterpret_cast<const unsigned*>(&Xs[r + 8][kk + 2 * t4]);
+      a[2] = *reinterpret_cast<const unsigned*>(&Xs[r][kk + 8 + 2 * t4]);
+      a[3] = *reinterpret_cast<const unsigned*>(&Xs[r + 8][kk + 8 + 2 * t4]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const unsigned b0 = *reinterpret_cast<const unsigned*>(&Ws[j * 8 + g][kk + 2 * t4]);
+        const unsigned b1 = *reinterpret_cast<const unsigned*>(&Ws[j * 8 + g][kk + 8 + 2 * t4]);
+        mma_bf16(acc[j], a, b0, b1);
+      }
+    }
+  }
+  pdl_launch_dependents();
+#pragma unroll
+  for (int half = 0; half < 2; ++half) {
+    const int m = m0 + warp * 16 + g + half * 8;
+    if (m >= T) continue;
+    const float gt = gate != nullptr ? 1.0f / (1.0f + expf(-gate[(size_t)m * ldg + goff + h])) : 1.0f;
+    __nv_bfloat16* o = out + (size_t)m * H * dout + (size_t)h * dout;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int n = n0 + j * 8 + 2 * t4;
+      if (n < dout) o[n] = __float2bfloat16_rn(acc[j][half * 2] * gt);
+      if (n + 1 < dout) o[n + 1] = __float2bfloat16_rn(acc[j][half * 2 + 1] * gt);
+    }
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -119,9 +209,19 @@ SLLM_EXPORT int sllm_head_linear(const void* x, int x_dtype, int ldx, int xoff, 
 #define SLLM_HL(TX, TW, TO)                                                                                              \
   launch_kernel(head_linear_kernel<TX, TW, TO>, grid, 256, 0, stream, (const TX*)x, ldx, xoff, (const TW*)w, (TO*)out, gate, ldg, \
                 goff, T, H, din, dout)
+  if (w_dtype == SLLM_BF16 && out_dtype == SLLM_BF16 && (x_dtype == SLLM_F32 || x_dtype == SLLM_BF16)) {
+    // the bfloat16 path: tensor cores; 16-byte loads where every row of x and of W starts on a 16-byte boundary
+    const int xe = x_dtype == SLLM_F32 ? 4 : 8;
+    const int vec = din % 8 == 0 && ldx % xe == 0 && xoff % xe == 0 && ((uintptr_t)x & 15) == 0 && ((uintptr_t)w & 15) == 0;
+    if (x_dtype == SLLM_F32)
+      launch_kernel(head_linear_mma_kernel<float>, grid, 128, 0, stream, (const float*)x, ldx, xoff, (const __nv_bfloat16*)w,
+                    (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec);
+    else
+      launch_kernel(head_linear_mma_kernel<__nv_bfloat16>, grid, 128, 0, stream, (const __nv_bfloat16*)x, ldx, xoff,
+                    (const __nv_bfloat16*)w, (__nv_bfloat16*)out, gate, ldg, goff, T, H, din, dout, vec);
+    return launch_status("head_linear");
+  }
   if (x_dtype == SLLM_F32 && w_dtype == SLLM_F32 && out_dtype == SLLM_F32) SLLM_HL(float, float, float);
-  else if (x_dtype == SLLM_F32 && w_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) SLLM_HL(float, __nv_bfloat16, __nv_bfloat16);
-  else if (x_dtype == SLLM_BF16 && w_dtype == SLLM_BF16 && out_dtype == SLLM_BF16) SLLM_HL(__nv_bfloat16, __nv_bfloat16, __nv_bfloat16);
   else SLLM_REQUIRE(false, "head_linear: dtypes x=%d w=%d out=%d", x_dtype, w_dtype, out_dtype);
 #undef SLLM_HL
   return launch_status("head_linear");

@@ -65,48 +65,123 @@ __global__ void add_group_ssq_kernel(float* __restrict__ stream, const float* __
   }
 }
 
+__device__ __forceinline__ float4 pb_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 pb_load4(const __nv_bfloat16* p) {
+  const uint2 raw = *reinterpret_cast<const uint2*>(p);
+  const __nv_bfloat162 a = *reinterpret_cast<const __nv_bfloat162*>(&raw.x);
+  const __nv_bfloat162 b = *reinterpret_cast<const __nv_bfloat162*>(&raw.y);
+  return make_float4(__low2float(a), __high2float(a), __low2float(b), __high2float(b));
+}
+__device__ __forceinline__ void pb_store4(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+__device__ __forceinline__ void pb_store4(__nv_bfloat16* p, float4 v) {
+  __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+  uint2 raw;
+  raw.x = *reinterpret_cast<unsigned*>(&a);
+  raw.y = *reinterpret_cast<unsigned*>(&b);
+  *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// 1 / sqrt(mean(x[group]^2) + eps) of every group of a row, into dst[groups] (shared memory): warps take groups in
+// turn; a group's sum is taken in an order that depends on its size only.
+template <bool VEC>
+__device__ __forceinline__ void group_roots(const float* __restrict__ row, float* dst, int groups, int gs, float eps) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  for (int g = warp; g < groups; g += nw) {
+    const float* x = row + (size_t)g * gs;
+    float ss = 0.f;
+    if constexpr (VEC) {
+      for (int i = lane * 4; i < gs; i += 128) {
+        const float4 v = pb_load4(x + i);
+        ss = fmaf(v.x, v.x, ss); ss = fmaf(v.y, v.y, ss); ss = fmaf(v.z, v.z, ss); ss = fmaf(v.w, v.w, ss);
+      }
+    } else {
+      for (int i = lane; i < gs; i += 32) ss = fmaf(x[i], x[i], ss);
+    }
+    ss = warp_sum(ss);
+    if (lane == 0) dst[g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
+}
+
 // h[t, i] = stream[t, i] * rinv[t, g(i)] * gain[i]                      -> out_h (if given)
 // hs[t, i] = h + (h_prev - h) * mix[i]                                   -> out_hs (if mix is given)
 // h_prev is the normed row t-1 of the same request's portion, or state[slot] for the portion's first
 // token; the block of that first token then writes the portion's last normed row to state[slot] (each
 // thread reads its channels of the slot before it writes them; no other block touches the slot).
-template <typename TO>
+// rinv == nullptr: the block takes the reciprocal roots of the rows it reads itself (the row, and the row
+// before or the portion's last), so that a stream with nothing pending needs no kernel before this one.
+// VEC: W and W / groups are multiples of 4 and every pointer is 16-byte aligned.
+template <typename TO, bool VEC>
 __global__ void group_norm_shift_kernel(const float* __restrict__ stream, const float* __restrict__ rinv,
                                         const float* __restrict__ gain, const float* __restrict__ mix,
                                         float* __restrict__ state, const int* __restrict__ seq_of_token,
                                         const int* __restrict__ q_start, const int* __restrict__ state_slots,
-                                        TO* __restrict__ out_h, TO* __restrict__ out_hs, int W, int groups) {
+                                        TO* __restrict__ out_h, TO* __restrict__ out_hs, int W, int groups, float eps) {
+  extern __shared__ float s_ri[];          // [2][groups]: this row's roots, and the other row's
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
   const int gs = W / groups;
   const float* row = stream + (size_t)t * W;
-  const float* ri = rinv + (size_t)t * groups;
-  if (mix == nullptr) {
-    for (int i = threadIdx.x; i < W; i += blockDim.x) out_h[(size_t)t * W + i] = from_f32<TO>(row[i] * ri[i / gs] * gain[i]);
-    return;
+  int first_t = t, last_t = t;
+  bool first = false;
+  float* slot = nullptr;
+  if (mix != nullptr) {
+    const int s = seq_of_token[t];
+    first_t = q_start[s];
+    last_t = q_start[s + 1] - 1;
+    first = t == first_t;
+    slot = state + (size_t)state_slots[s] * W;
   }
-  const int s = seq_of_token[t];
-  const int first_t = q_start[s], last_t = q_start[s + 1] - 1;
-  const bool first = t == first_t;
-  float* slot = state + (size_t)state_slots[s] * W;
-  const float* prow = row - W;
-  const float* pri = ri - groups;
-  const float* lrow = stream + (size_t)last_t * W;
-  const float* lri = rinv + (size_t)last_t * groups;
-  for (int i = threadIdx.x; i < W; i += blockDim.x) {
-    const int g = i / gs;
-    const float w = gain[i];
-    const float h = row[i] * ri[g] * w;
-    float hp;
-    if (first) {
-      hp = slot[i];
-      slot[i] = lrow[i] * lri[g] * w;
-    } else {
-      hp = prow[i] * pri[g] * w;
+  // the other row: the one before (its normed form is h_prev), or for a portion's first token the portion's last
+  const int other_t = mix == nullptr ? t : (first ? last_t : t - 1);
+  const float* orow = stream + (size_t)other_t * W;
+  const float* ri;
+  const float* ori;
+  if (rinv != nullptr) {
+    ri = rinv + (size_t)t * groups;
+    ori = rinv + (size_t)other_t * groups;
+  } else {
+    group_roots<VEC>(row, s_ri, groups, gs, eps);
+    if (other_t != t) group_roots<VEC>(orow, s_ri + groups, groups, gs, eps);
+    __syncthreads();
+    ri = s_ri;
+    ori = other_t != t ? s_ri + groups : s_ri;
+  }
+  if constexpr (VEC) {
+    for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+      const int g = i / gs;
+      const float4 x = pb_load4(row + i), w = pb_load4(gain + i);
+      const float r = ri[g];
+      const float4 h = make_float4(x.x * r * w.x, x.y * r * w.y, x.z * r * w.z, x.w * r * w.w);
+      if (out_h != nullptr) pb_store4(out_h + (size_t)t * W + i, h);
+      if (mix == nullptr) continue;
+      const float4 ox = pb_load4(orow + i);
+      const float orr = ori[g];
+      const float4 oh = make_float4(ox.x * orr * w.x, ox.y * orr * w.y, ox.z * orr * w.z, ox.w * orr * w.w);
+      float4 hp = oh;
+      if (first) {
+        hp = pb_load4(slot + i);
+        pb_store4(slot + i, oh);
+      }
+      const float4 m = pb_load4(mix + i);
+      pb_store4(out_hs + (size_t)t * W + i, make_float4(h.x + (hp.x - h.x) * m.x, h.y + (hp.y - h.y) * m.y,
+                                                        h.z + (hp.z - h.z) * m.z, h.w + (hp.w - h.w) * m.w));
     }
-    if (out_h != nullptr) out_h[(size_t)t * W + i] = from_f32<TO>(h);
-    out_hs[(size_t)t * W + i] = from_f32<TO>(h + (hp - h) * mix[i]);
+  } else {
+    for (int i = threadIdx.x; i < W; i += blockDim.x) {
+      const int g = i / gs;
+      const float w = gain[i];
+      const float h = row[i] * ri[g] * w;
+      if (out_h != nullptr) out_h[(size_t)t * W + i] = from_f32<TO>(h);
+      if (mix == nullptr) continue;
+      const float oh = orow[i] * ori[g] * w;
+      float hp = oh;
+      if (first) {
+        hp = slot[i];
+        slot[i] = oh;
+      }
+      out_hs[(size_t)t * W + i] = from_f32<TO>(h + (hp - h) * mix[i]);
+    }
   }
 }
 
@@ -116,17 +191,29 @@ __device__ __forceinline__ float act_gelu_tanh(float z) {
 }
 
 // out[t, i] = act(gate) * up; gate and up alternate along a row of gu in blocks of `interleave` columns
-// (interleave == I: all gates, then all ups).
-template <typename TI, typename TO, int ACT>
+// (interleave == I: all gates, then all ups).  VEC: I and interleave are multiples of 4 and the pointers 16-byte
+// aligned; four results a thread.
+template <typename TI, typename TO, int ACT, bool VEC>
 __global__ void act_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int interleave) {
   pdl_launch_dependents();
   pdl_wait();
   const size_t t = blockIdx.y;
-  for (int i = blockIdx.x * blockDim.x + threadIdx.x; i < I; i += gridDim.x * blockDim.x) {
+  constexpr int PER = VEC ? 4 : 1;
+  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * PER; i < I; i += gridDim.x * blockDim.x * PER) {
     const int b = i / interleave, o = i % interleave;
     const TI* p = gu + t * 2 * I + (size_t)b * 2 * interleave + o;
-    const float g = to_f32(p[0]), u = to_f32(p[interleave]);
-    out[t * I + i] = from_f32<TO>((ACT == 0 ? act_silu(g) : act_gelu_tanh(g)) * u);
+    if constexpr (VEC) {
+      const float4 g = pb_load4(p), u = pb_load4(p + interleave);
+      float4 r;
+      r.x = (ACT == 0 ? act_silu(g.x) : act_gelu_tanh(g.x)) * u.x;
+      r.y = (ACT == 0 ? act_silu(g.y) : act_gelu_tanh(g.y)) * u.y;
+      r.z = (ACT == 0 ? act_silu(g.z) : act_gelu_tanh(g.z)) * u.z;
+      r.w = (ACT == 0 ? act_silu(g.w) : act_gelu_tanh(g.w)) * u.w;
+      pb_store4(out + t * I + i, r);
+    } else {
+      const float g = to_f32(p[0]), u = to_f32(p[interleave]);
+      out[t * I + i] = from_f32<TO>((ACT == 0 ? act_silu(g) : act_gelu_tanh(g)) * u);
+    }
   }
 }
 
@@ -166,20 +253,24 @@ SLLM_EXPORT int sllm_add_group_ssq(float* stream, const float* d0, int parts0, s
 
 SLLM_EXPORT int sllm_group_norm_shift(const float* stream, const float* rinv, const float* gain, const float* mix, float* state,
                                       const int* seq_of_token, const int* q_start, const int* state_slots, void* out_h,
-                                      void* out_hs, int out_dtype, int T, int W, int groups, cudaStream_t stream_) {
+                                      void* out_hs, int out_dtype, int T, int W, int groups, float eps, cudaStream_t stream_) {
   SLLM_REQUIRE(T >= 0 && W > 0 && groups > 0 && W % groups == 0, "group_norm_shift: %d groups do not divide the width %d", groups, W);
   SLLM_REQUIRE(mix != nullptr ? (state && seq_of_token && q_start && state_slots && out_hs) : (out_h != nullptr),
                "group_norm_shift: a shift needs its state, the batch's description and an output; a plain norm needs an output");
+  SLLM_REQUIRE(groups <= 4096, "group_norm_shift: %d groups", groups);
   if (T == 0) return SLLM_OK;
   const int threads = W >= 2048 ? 256 : 128;
-  if (out_dtype == SLLM_F32)
-    launch_kernel(group_norm_shift_kernel<float>, T, threads, 0, stream_, stream, rinv, gain, mix, state, seq_of_token, q_start,
-                  state_slots, (float*)out_h, (float*)out_hs, W, groups);
-  else if (out_dtype == SLLM_BF16)
-    launch_kernel(group_norm_shift_kernel<__nv_bfloat16>, T, threads, 0, stream_, stream, rinv, gain, mix, state, seq_of_token,
-                  q_start, state_slots, (__nv_bfloat16*)out_h, (__nv_bfloat16*)out_hs, W, groups);
-  else
-    SLLM_REQUIRE(false, "group_norm_shift: unknown dtype %d", out_dtype);
+  const size_t smem = 2 * (size_t)groups * sizeof(float);
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = W % 4 == 0 && (W / groups) % 4 == 0 && aligned(stream) && aligned(gain) && aligned(mix) && aligned(state) &&
+                   aligned(out_h) && aligned(out_hs);
+#define SLLM_GNS(TO, VEC_)                                                                                                 \
+  launch_kernel(group_norm_shift_kernel<TO, VEC_>, T, threads, smem, stream_, stream, rinv, gain, mix, state, seq_of_token, \
+                q_start, state_slots, (TO*)out_h, (TO*)out_hs, W, groups, eps)
+  if (out_dtype == SLLM_F32) { if (vec) SLLM_GNS(float, true); else SLLM_GNS(float, false); }
+  else if (out_dtype == SLLM_BF16) { if (vec) SLLM_GNS(__nv_bfloat16, true); else SLLM_GNS(__nv_bfloat16, false); }
+  else SLLM_REQUIRE(false, "group_norm_shift: unknown dtype %d", out_dtype);
+#undef SLLM_GNS
   return launch_status("group_norm_shift");
 }
 
@@ -188,12 +279,16 @@ SLLM_EXPORT int sllm_act_mul(const void* gu, int in_dtype, void* out, int out_dt
   SLLM_REQUIRE(T >= 0 && I > 0 && interleave > 0 && I % interleave == 0, "act_mul: bad sizes T=%d I=%d interleave=%d", T, I, interleave);
   SLLM_REQUIRE(act == 0 || act == 1, "act_mul: activation %d is neither 0 (silu) nor 1 (gelu_tanh)", act);
   if (T == 0) return SLLM_OK;
-  const dim3 grid((unsigned)((I + 255) / 256 > 64 ? 64 : (I + 255) / 256), (unsigned)T);
+  const int per_block = 256 * 4;
+  const dim3 grid((unsigned)((I + per_block - 1) / per_block > 64 ? 64 : (I + per_block - 1) / per_block), (unsigned)T);
   SLLM_REQUIRE(T <= 65535, "act_mul: more than 65535 rows in one launch");
-#define SLLM_ACT_MUL(TI, TO)                                                                                              \
-  do {                                                                                                                    \
-    if (act == 0) launch_kernel(act_mul_kernel<TI, TO, 0>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave); \
-    else launch_kernel(act_mul_kernel<TI, TO, 1>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);          \
+  const bool vec = I % 4 == 0 && interleave % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0;
+#define SLLM_ACT_MUL(TI, TO)                                                                                                       \
+  do {                                                                                                                             \
+    if (act == 0 && vec) launch_kernel(act_mul_kernel<TI, TO, 0, true>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);  \
+    else if (act == 0) launch_kernel(act_mul_kernel<TI, TO, 0, false>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);  \
+    else if (vec) launch_kernel(act_mul_kernel<TI, TO, 1, true>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);   \
+    else launch_kernel(act_mul_kernel<TI, TO, 1, false>, grid, 256, 0, stream_, (const TI*)gu, (TO*)out, I, interleave);           \
   } while (0)
   if (in_dtype == SLLM_F32 && out_dtype == SLLM_F32) SLLM_ACT_MUL(float, float);
   else if (in_dtype == SLLM_F32 && out_dtype == SLLM_BF16) SLLM_ACT_MUL(float, __nv_bfloat16);

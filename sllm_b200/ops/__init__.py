@@ -112,22 +112,24 @@ def add_group_ssq(stream: torch.Tensor, terms, groups: int, eps: float, want_rin
     return rinv
 
 
-def group_norm_shift(stream, rinv, gain, out_dtype, *, mix=None, state=None, step=None, want_plain: bool = True):
-    """The norm in groups applied: ``h = stream * rinv[group] * gain`` in ``out_dtype``.  With ``mix``: also the
-    mixer's input ``hs = h + (h_prev - h) * mix``, ``h_prev`` the same request's row before (for the first token
-    of its portion, the request's row of ``state`` ``[slots, W]``, which then receives the portion's last ``h``).
-    Returns ``h``, or ``(h, hs)`` (``h`` None if not wanted)."""
+def group_norm_shift(stream, rinv, gain, out_dtype, *, groups: int | None = None, eps: float = 0.0, mix=None, state=None,
+                     step=None, want_plain: bool = True):
+    """The norm in groups applied: ``h = stream * rinv[group] * gain`` in ``out_dtype``; with ``rinv`` None the kernel
+    takes the reciprocal roots itself (``groups``, ``eps``), so a stream with nothing pending needs one kernel.  With
+    ``mix``: also the mixer's input ``hs = h + (h_prev - h) * mix``, ``h_prev`` the same request's row before (for the
+    first token of its portion, the request's row of ``state`` ``[slots, W]``, which then receives the portion's last
+    ``h``).  Returns ``h``, or ``(h, hs)`` (``h`` None if not wanted)."""
     _chk(stream, rinv, gain, mix, state)
     T, W = stream.shape
-    groups = rinv.shape[1]
+    groups = int(rinv.shape[1] if rinv is not None else groups)
     h = torch.empty((T, W), dtype=out_dtype, device=stream.device) if (want_plain or mix is None) else None
     if mix is None:
         call("sllm_group_norm_shift", _p(stream), _p(rinv), _p(gain), None, None, None, None, None, _p(h), None,
-             _dtc(out_dtype), T, W, groups, _stream())
+             _dtc(out_dtype), T, W, groups, float(eps), _stream())
         return h
     hs = torch.empty((T, W), dtype=out_dtype, device=stream.device)
     call("sllm_group_norm_shift", _p(stream), _p(rinv), _p(gain), _p(mix), _p(state), _p(step.seq_of_token), _p(step.q_start),
-         _p(step.state_slots), _p(h), _p(hs), _dtc(out_dtype), T, W, groups, _stream())
+         _p(step.state_slots), _p(h), _p(hs), _dtc(out_dtype), T, W, groups, float(eps), _stream())
     return h, hs
 
 

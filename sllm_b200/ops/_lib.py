@@ -44,7 +44,7 @@ def _declare(L):
         "sllm_add_group_ssq": [c_void_p, c_void_p, c_int, c_size_t, c_void_p, c_int, c_size_t, c_void_p, c_int, c_int, c_int, c_float,
                                c_void_p],
         "sllm_group_norm_shift": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                                  c_int, c_int, c_int, c_int, c_void_p],
+                                  c_int, c_int, c_int, c_int, c_float, c_void_p],
         "sllm_act_mul": [c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "sllm_tanh_cols": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
         "sllm_delta_rule_supports": [c_int, c_int],

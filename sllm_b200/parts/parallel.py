@@ -38,13 +38,16 @@ class GroupRMSNorm(Norm):
     def bind(self, fetch):
         self.weight = self._f32(fetch(""))
 
-    def sum_squares(self, residual, terms):
-        """Add the pending terms into the stream; the reciprocal roots per row and group."""
-        return ops.add_group_ssq(residual, terms, self.groups, self.eps)
+    def complete(self, residual, delta) -> None:
+        """Add what a block before has left pending into the stream (nothing to do when its products added their
+        terms themselves)."""
+        terms = pending_terms(delta)
+        if terms:
+            ops.add_group_ssq(residual, terms, self.groups, self.eps, want_rinv=False)
 
     def add_norm(self, residual, delta):
-        rinv = self.sum_squares(residual, pending_terms(delta))
-        return ops.group_norm_shift(residual, rinv, self.weight, self.dtype)
+        self.complete(residual, delta)
+        return ops.group_norm_shift(residual, None, self.weight, self.dtype, groups=self.groups, eps=self.eps)
 
     def weight_bytes(self):
         return self.size * 4
@@ -164,12 +167,13 @@ class ParallelShiftBlock:
 
     def forward(self, residual, delta, step, cache, position, write_cache=True, next_norm=None):
         norm = self.norm
-        rinv = norm.sum_squares(residual, pending_terms(delta))
+        norm.complete(residual, delta)
+        kw = dict(groups=norm.groups, eps=norm.eps)
         if self.shift is not None:
-            h, hs = ops.group_norm_shift(residual, rinv, norm.weight, norm.dtype, mix=self.shift.mix,
-                                         state=cache.states["shift"], step=step, want_plain=self.ffn is not None)
+            h, hs = ops.group_norm_shift(residual, None, norm.weight, norm.dtype, mix=self.shift.mix,
+                                         state=cache.states["shift"], step=step, want_plain=self.ffn is not None, **kw)
         else:
-            h = hs = ops.group_norm_shift(residual, rinv, norm.weight, norm.dtype)
+            h = hs = ops.group_norm_shift(residual, None, norm.weight, norm.dtype, **kw)
         kw = {"residual": residual} if getattr(self.mixer, "accepts_residual", False) else {}
         terms = [self.mixer.forward(hs, step, cache, position, write_cache, **kw)]
         if self.ffn is not None:

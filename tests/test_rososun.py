@@ -163,7 +163,7 @@ def test_sinusoid_and_scaled_embedding(dev):
     np.testing.assert_allclose(x.cpu().numpy()[:4], want[:4], atol=1e-5)
 
 
-@pytest.mark.parametrize("groups", [1, 4, 6])
+@pytest.mark.parametrize("groups", [1, 4, 6, 16])
 def test_group_norm_with_pending_terms_and_token_shift_across_portions(dev, groups):
     import sllm_b200.ops as ops
     rng = np.random.default_rng(groups)
@@ -192,6 +192,13 @@ def test_group_norm_with_pending_terms_and_token_shift_across_portions(dev, grou
     np.testing.assert_allclose(state.cpu().numpy()[[2, 5]], before[[2, 5]], rtol=1e-6)                   # slots of nobody stay
     only = ops.group_norm_shift(stream, rinv, to(gain), torch.float32)
     np.testing.assert_allclose(only.cpu().numpy(), want_h, rtol=2e-5, atol=2e-5)
+    # the same with the reciprocal roots taken by the kernel itself, from fresh slots
+    state2 = to(before)
+    h2, hs2 = ops.group_norm_shift(stream, None, to(gain), torch.float32, groups=groups, eps=eps, mix=to(mix), state=state2,
+                                   step=_step(dev, lens, slots))
+    np.testing.assert_allclose(h2.cpu().numpy(), want_h, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(hs2.cpu().numpy(), hs.cpu().numpy(), rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(state2.cpu().numpy(), state.cpu().numpy(), rtol=2e-5, atol=2e-5)
 
 
 def test_gated_activation(dev):
@@ -207,7 +214,7 @@ def test_gated_activation(dev):
     np.testing.assert_allclose(got, np.tanh(gu[:, 5:16]), rtol=1e-5, atol=1e-6)
 
 
-@pytest.mark.parametrize("heads,dk", [(1, 64), (3, 16), (2, 40), (1, 130)])
+@pytest.mark.parametrize("heads,dk", [(1, 64), (3, 16), (2, 40), (1, 130), (80, 16), (2, 6)])
 def test_delta_rule_recurrence_in_portions_and_slots(dev, heads, dk):
     """The recurrence alone: two requests side by side, each cut into portions (down to one token) that continue from
     the state slot, against the whole sequences through the plain recurrence."""
@@ -258,6 +265,18 @@ def test_head_products_and_latent_write(dev):
     got = ops.head_linear(to(x), 7, to(w), torch.float32, gate=to(x), goff=80).cpu().numpy()
     want = np.einsum("thi,hoi->tho", x[:, 7:7 + H * din].reshape(T, H, din), w) * plain.sigmoid(x[:, 80:80 + H])[:, :, None]
     np.testing.assert_allclose(got, want.reshape(T, H * dout), rtol=1e-4, atol=1e-4)
+    # bfloat16 operands (the tensor-core form on the GPU): x in float32 or bfloat16, rows that allow 16-byte loads and
+    # rows that do not, sizes that end inside a tile
+    for T2, H2, din2, dout2, xoff2 in ((70, 3, 20, 24, 7), (150, 2, 64, 96, 8), (9, 5, 128, 40, 0)):
+        ld2 = xoff2 + H2 * din2 + 16
+        x2 = rng.standard_normal((T2, ld2))
+        w2 = rng.standard_normal((H2, dout2, din2)) * 0.3
+        wb = to(w2).to(torch.bfloat16)
+        for xt in (to(x2), to(x2).to(torch.bfloat16)):
+            got = ops.head_linear(xt, xoff2, wb, torch.bfloat16, gate=to(x2), goff=ld2 - H2).float().cpu().numpy()
+            xs = xt.to(torch.bfloat16).double().cpu().numpy()[:, xoff2:xoff2 + H2 * din2].reshape(T2, H2, din2)
+            want = np.einsum("thi,hoi->tho", xs, wb.double().cpu().numpy()) * plain.sigmoid(x2[:, ld2 - H2:])[:, :, None]
+            np.testing.assert_allclose(got, want.reshape(T2, H2 * dout2), rtol=1e-2, atol=1e-2)
     rank, ps = 24, 4
     cache = torch.zeros((30, 1, ps, rank), dtype=torch.float32, device=dev)
     gain = 1 + 0.2 * rng.standard_normal(rank)

@@ -34,8 +34,10 @@ def add_group_ssq(stream, terms, groups, eps, want_rinv=True):
     return (stream.reshape(T, groups, W // groups).pow(2).mean(-1) + eps).rsqrt()
 
 
-def group_norm_shift(stream, rinv, gain, out_dtype, *, mix=None, state=None, step=None, want_plain=True):
+def group_norm_shift(stream, rinv, gain, out_dtype, *, groups=None, eps=0.0, mix=None, state=None, step=None, want_plain=True):
     T, W = stream.shape
+    if rinv is None:
+        rinv = (stream.reshape(T, groups, W // groups).pow(2).mean(-1) + eps).rsqrt()
     groups = rinv.shape[1]
     h = (stream.reshape(T, groups, W // groups) * rinv[:, :, None]).reshape(T, W) * gain
     if mix is None:
@@ -109,7 +111,7 @@ def latent_write(proj, off, rank, gain, eps, slot_mapping, cache):
 def head_linear(x, xoff, w, out_dtype, *, gate=None, goff=0):
     H, dout, din = w.shape
     T = x.shape[0]
-    xs = x[:, xoff:xoff + H * din].float().reshape(T, H, din)
+    xs = x[:, xoff:xoff + H * din].to(w.dtype).float().reshape(T, H, din)      # (operands in the matrix's dtype)
     out = torch.einsum("thi,hoi->tho", xs, w.float())
     if gate is not None:
         out = out * torch.sigmoid(gate[:, goff:goff + H])[:, :, None]
