@@ -9,10 +9,12 @@
 // outputs are float32.
 //
 // The columns of S evolve independently of one another (column j needs u, d, a*u, k, r of the token and
-// v_j only), so a CTA owns a slice of 64 columns of one (request, head) and walks the request's tokens in
-// order.  Eight consecutive lanes share four columns, each lane holding every eighth row of them in registers
-// (a token's five vectors are read from shared memory once per four columns); the two sums over rows of a
-// step end in shuffles among the eight.  Four warps compute; four more prepare the next chunk of tokens in the
+// v_j only), so a CTA owns a slice of 16 CB columns of one (request, head) and walks the request's tokens in
+// order.  Eight consecutive lanes share CB columns, each lane holding every eighth row of them in registers; the
+// two sums over rows of a step end in shuffles among the eight.  CB = 4 (a token's five vectors are read from
+// shared memory once per four columns: a quarter of the shared-memory reads and of the CTAs) when the batch has
+// enough (request, head) pairs to fill the device; CB = 1 when it has not: four times the CTAs, a quarter of the
+// work per lane and token, so that one long prompt's walk is as short as it gets.  Four warps compute; four more prepare the next chunk of tokens in the
 // other half of shared memory meanwhile (unit keys, decays, rates: a warp per token, all of a token's loads in
 // flight at once), so the walk never waits for global memory: one CTA-wide barrier per chunk, none per token.
 // A portion of a prompt and a single decoded token run through the same kernel, from the state slot and back
@@ -38,15 +40,16 @@ struct DeltaParams {
   const int* q_start;      // [S+1]
   const int* state_slots;  // [S]
   float* out;              // [T, H*dv]
-  int ld, off_r, off_k, off_v, off_a, H, dk, dv, chunk;
+  int ld, off_r, off_k, off_v, off_a, H, dk, dv, chunk, max_q;
 };
 
 // RPT: rows of a column per lane (dk <= 8 * RPT = DKP, the padded key size).
-constexpr int DR_SPLIT = 8, DR_CB = 4, DR_COLS = DR_COMPUTE / DR_SPLIT * DR_CB;      // 64 columns a CTA
+constexpr int DR_SPLIT = 8;
 
-template <int RPT>
+template <int RPT, int CB>
 __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParams p) {
-  constexpr int SPLIT = DR_SPLIT, CB = DR_CB, COLS = DR_COLS, DKP = RPT * SPLIT, PER_LANE = (DKP + 31) / 32;
+  constexpr int SPLIT = DR_SPLIT, COLS = DR_COMPUTE / SPLIT * CB, DKP = RPT * SPLIT, PER_LANE = (DKP + 31) / 32;
+  constexpr int VPL = (COLS + 31) / 32;       // values of v a loader lane brings
   extern __shared__ __align__(16) float sm[];
   const int dk = p.dk, dv = p.dv, chunk = p.chunk;
   const int buf_floats = chunk * (5 * DKP + COLS);
@@ -64,27 +67,38 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
     float* s_v = b + 5 * chunk * DKP;
     const int t0 = t_begin + c * chunk, nt = min(chunk, t_end - t0);
     const float c_decay = -expf(-0.5f);
-    for (int tt = (tid - DR_COMPUTE) >> 5; tt < nt; tt += DR_COMPUTE / 32) {
-      const float* row = p.proj + (size_t)(t0 + tt) * p.ld;
-      const float* dec = p.decay + (size_t)(t0 + tt) * p.H * dk + h * dk;
-      float k[PER_LANE], a[PER_LANE], d[PER_LANE], r[PER_LANE], v[COLS / 32];
-      float ss = 0.f;
+    constexpr int TPW = DR_MAX_CHUNK / (DR_COMPUTE / 32);       // tokens of a chunk per loader warp
+    const int lw = (tid - DR_COMPUTE) >> 5;
+    float k[TPW][PER_LANE], a[TPW][PER_LANE], d[TPW][PER_LANE], r[TPW][PER_LANE], v[TPW][VPL];
+    // every load of the warp's tokens first, then the arithmetic: the loads of all of them are in flight together
+#pragma unroll
+    for (int q = 0; q < TPW; ++q) {
+      const int tt = lw + q * (DR_COMPUTE / 32);
+      const bool tok = tt < nt;
+      const float* row = p.proj + (size_t)(t0 + (tok ? tt : 0)) * p.ld;
+      const float* dec = p.decay + (size_t)(t0 + (tok ? tt : 0)) * p.H * dk + h * dk;
 #pragma unroll
       for (int m = 0; m < PER_LANE; ++m) {
         const int i = lane + 32 * m;
-        const bool in = i < dk;
-        k[m] = in ? __ldg(row + p.off_k + h * dk + i) : 0.f;
-        a[m] = in ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
-        d[m] = in ? __ldg(dec + i) : 0.f;
-        r[m] = in ? __ldg(row + p.off_r + h * dk + i) : 0.f;
+        const bool in = tok && i < dk;
+        k[q][m] = in ? __ldg(row + p.off_k + h * dk + i) : 0.f;
+        a[q][m] = in ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
+        d[q][m] = in ? __ldg(dec + i) : 0.f;
+        r[q][m] = in ? __ldg(row + p.off_r + h * dk + i) : 0.f;
       }
 #pragma unroll
-      for (int m = 0; m < COLS / 32; ++m) {
+      for (int m = 0; m < VPL; ++m) {
         const int j = c0 + lane + 32 * m;
-        v[m] = j < dv ? __ldg(row + p.off_v + h * dv + j) : 0.f;
+        v[q][m] = (tok && lane + 32 * m < COLS && j < dv) ? __ldg(row + p.off_v + h * dv + j) : 0.f;
       }
+    }
 #pragma unroll
-      for (int m = 0; m < PER_LANE; ++m) ss = fmaf(k[m], k[m], ss);
+    for (int q = 0; q < TPW; ++q) {
+      const int tt = lw + q * (DR_COMPUTE / 32);
+      if (tt >= nt) break;
+      float ss = 0.f;
+#pragma unroll
+      for (int m = 0; m < PER_LANE; ++m) ss = fmaf(k[q][m], k[q][m], ss);
       ss = warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss + 1e-6f);
 #pragma unroll
@@ -92,31 +106,38 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         const int i = lane + 32 * m;
         if (i < DKP) {
           const bool in = i < dk;
-          const float u = k[m] * inv;
-          s_k[tt * DKP + i] = k[m];
+          const float u = k[q][m] * inv;
+          s_k[tt * DKP + i] = k[q][m];
           s_u[tt * DKP + i] = u;
-          s_au[tt * DKP + i] = in ? sigmoidf_(a[m]) * u : 0.f;
-          s_d[tt * DKP + i] = in ? expf(c_decay * sigmoidf_(d[m])) : 0.f;
-          s_r[tt * DKP + i] = r[m];
+          s_au[tt * DKP + i] = in ? sigmoidf_(a[q][m]) * u : 0.f;
+          s_d[tt * DKP + i] = in ? expf(c_decay * sigmoidf_(d[q][m])) : 0.f;
+          s_r[tt * DKP + i] = r[q][m];
         }
       }
 #pragma unroll
-      for (int m = 0; m < COLS / 32; ++m) s_v[tt * COLS + lane + 32 * m] = v[m];
+      for (int m = 0; m < VPL; ++m)
+        if (lane + 32 * m < COLS) s_v[tt * COLS + lane + 32 * m] = v[q][m];
     }
   };
 
-  const int cg = (tid % DR_COMPUTE) / SPLIT, rs = tid % SPLIT;     // this lane's four columns c0 + 4 cg .., its rows rs + 8 n
+  const int cg = (tid % DR_COMPUTE) / SPLIT, rs = tid % SPLIT;     // this lane's columns c0 + CB cg .., its rows rs + 8 n
   const int col = c0 + cg * CB;
   float* S = p.state + ((size_t)p.state_slots[seq] * p.H + h) * dk * dv;
   float s[RPT][CB];
   if (loader) {
     if (nchunks > 0) prepare(0);
   } else {
+    const bool vec_state = CB == 4 && dv % 4 == 0 && ((uintptr_t)S & 15) == 0;
 #pragma unroll
     for (int n = 0; n < RPT; ++n) {
       const int i = n * SPLIT + rs;
+      if (vec_state) {
+        const float4 x = (i < dk && col < dv) ? *reinterpret_cast<const float4*>(S + (size_t)i * dv + col) : make_float4(0.f, 0.f, 0.f, 0.f);
+        s[n][0] = x.x; s[n][CB > 1 ? 1 : 0] = x.y; s[n][CB > 2 ? 2 : 0] = x.z; s[n][CB > 3 ? 3 : 0] = x.w;
+      } else {
 #pragma unroll
-      for (int c = 0; c < CB; ++c) s[n][c] = (i < dk && col + c < dv) ? S[(size_t)i * dv + col + c] : 0.f;
+        for (int c = 0; c < CB; ++c) s[n][c] = (i < dk && col + c < dv) ? S[(size_t)i * dv + col + c] : 0.f;
+      }
     }
   }
   __syncthreads();
@@ -133,8 +154,16 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         const float* au = d + chunk * DKP;
         const float* k = au + chunk * DKP;
         const float* r = k + chunk * DKP;
-        const float4 v = *reinterpret_cast<const float4*>(b + 5 * chunk * DKP + tt * COLS + cg * CB);
-        float us[CB] = {0.f, 0.f, 0.f, 0.f}, ut[CB] = {0.f, 0.f, 0.f, 0.f};
+        float vv[CB], us[CB], ut[CB], o[CB], o2[CB];
+        if constexpr (CB == 4) {
+          const float4 v = *reinterpret_cast<const float4*>(b + 5 * chunk * DKP + tt * COLS + cg * CB);
+          vv[0] = v.x; vv[1] = v.y; vv[2] = v.z; vv[3] = v.w;
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < CB; ++cc) vv[cc] = b[5 * chunk * DKP + tt * COLS + cg * CB + cc];
+        }
+#pragma unroll
+        for (int cc = 0; cc < CB; ++cc) us[cc] = ut[cc] = o[cc] = o2[cc] = 0.f;
 #pragma unroll
         for (int n = 0; n < RPT; n += 2) {
           const float ua = u[n * SPLIT], ub = u[(n + 1) * SPLIT];
@@ -150,8 +179,6 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
 #pragma unroll
           for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
         }
-        const float vv[CB] = {v.x, v.y, v.z, v.w};
-        float o[CB] = {0.f, 0.f, 0.f, 0.f}, o2[CB] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
         for (int n = 0; n < RPT; n += 2) {
           const float ka = k[n * SPLIT], kb = k[(n + 1) * SPLIT], aa = -au[n * SPLIT], ab = -au[(n + 1) * SPLIT];
@@ -164,27 +191,43 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
             o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
           }
         }
-        // the four sums over eight lanes in four shuffles: halves of the values change hands, then quarters; lane rs
-        // ends with the whole sum of column 2 (rs & 1) + ((rs >> 1) & 1)
-        const bool odd = rs & 1, hi = rs & 2;
-        float a0 = (odd ? o[2] + o2[2] : o[0] + o2[0]) + __shfl_xor_sync(0xffffffffu, odd ? o[0] + o2[0] : o[2] + o2[2], 1);
-        float a1 = (odd ? o[3] + o2[3] : o[1] + o2[1]) + __shfl_xor_sync(0xffffffffu, odd ? o[1] + o2[1] : o[3] + o2[3], 1);
-        float tot = (hi ? a1 : a0) + __shfl_xor_sync(0xffffffffu, hi ? a0 : a1, 2);
-        tot += __shfl_xor_sync(0xffffffffu, tot, 4);
-        const int mine = col + 2 * (rs & 1) + ((rs >> 1) & 1);
-        if (rs < 4 && mine < dv) p.out[(size_t)(t0 + tt) * p.H * dv + h * dv + mine] = tot;
+        if constexpr (CB == 4) {
+          // the four sums over eight lanes in four shuffles: halves of the values change hands, then quarters; lane rs
+          // ends with the whole sum of column 2 (rs & 1) + ((rs >> 1) & 1)
+          const bool odd = rs & 1, hi = rs & 2;
+          float a0 = (odd ? o[2] + o2[2] : o[0] + o2[0]) + __shfl_xor_sync(0xffffffffu, odd ? o[0] + o2[0] : o[2] + o2[2], 1);
+          float a1 = (odd ? o[3] + o2[3] : o[1] + o2[1]) + __shfl_xor_sync(0xffffffffu, odd ? o[1] + o2[1] : o[3] + o2[3], 1);
+          float tot = (hi ? a1 : a0) + __shfl_xor_sync(0xffffffffu, hi ? a0 : a1, 2);
+          tot += __shfl_xor_sync(0xffffffffu, tot, 4);
+          const int mine = col + 2 * (rs & 1) + ((rs >> 1) & 1);
+          if (rs < 4 && mine < dv) p.out[(size_t)(t0 + tt) * p.H * dv + h * dv + mine] = tot;
+        } else {
+#pragma unroll
+          for (int cc = 0; cc < CB; ++cc) {
+            float tot = o[cc] + o2[cc];
+#pragma unroll
+            for (int w = 1; w < SPLIT; w <<= 1) tot += __shfl_xor_sync(0xffffffffu, tot, w);
+            if (rs == 0 && col + cc < dv) p.out[(size_t)(t0 + tt) * p.H * dv + h * dv + col + cc] = tot;
+          }
+        }
       }
     }
     __syncthreads();
   }
   pdl_launch_dependents();
   if (!loader) {
+    const bool vec_state = CB == 4 && dv % 4 == 0 && ((uintptr_t)S & 15) == 0;
 #pragma unroll
     for (int n = 0; n < RPT; ++n) {
       const int i = n * SPLIT + rs;
+      if (vec_state) {
+        if (i < dk && col < dv)
+          *reinterpret_cast<float4*>(S + (size_t)i * dv + col) = make_float4(s[n][0], s[n][CB > 1 ? 1 : 0], s[n][CB > 2 ? 2 : 0], s[n][CB > 3 ? 3 : 0]);
+      } else {
 #pragma unroll
-      for (int cc = 0; cc < CB; ++cc)
-        if (i < dk && col + cc < dv) S[(size_t)i * dv + col + cc] = s[n][cc];
+        for (int cc = 0; cc < CB; ++cc)
+          if (i < dk && col + cc < dv) S[(size_t)i * dv + col + cc] = s[n][cc];
+      }
     }
   }
 }
@@ -215,17 +258,18 @@ using namespace sllm;
 
 SLLM_EXPORT int sllm_delta_rule_supports(int dk, int dv) { return dk >= 1 && dk <= 256 && dv >= 1 && dv <= 65535 * 16; }
 
-template <int RPT>
+template <int RPT, int CB>
 static int launch_delta_rule(DeltaParams p, int S, cudaStream_t stream) {
-  constexpr int DKP = RPT * DR_SPLIT;
+  constexpr int DKP = RPT * DR_SPLIT, DR_COLS = DR_COMPUTE / DR_SPLIT * CB;
   const size_t per_token = (size_t)(5 * DKP + DR_COLS) * sizeof(float);
   int chunk = (int)((96 * 1024) / (2 * per_token));
   chunk = chunk > DR_MAX_CHUNK ? DR_MAX_CHUNK : (chunk < 1 ? 1 : chunk);
+  if (p.max_q > 0 && chunk > p.max_q) chunk = p.max_q;      // single decoded tokens: little shared memory, more CTAs an SM
   p.chunk = chunk;
   const size_t smem = 2 * per_token * chunk;
   static size_t allowed = 48 * 1024;          // (per instantiation: what the kernel has been told it may use)
   if (smem > allowed) {
-    if (cudaFuncSetAttribute(delta_rule_kernel<RPT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
+    if (cudaFuncSetAttribute(delta_rule_kernel<RPT, CB>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) != cudaSuccess) {
       cudaGetLastError();
       set_error("delta_rule: the kernel's shared memory could not be raised");
       return SLLM_ERR_LAUNCH;
@@ -233,13 +277,13 @@ static int launch_delta_rule(DeltaParams p, int S, cudaStream_t stream) {
     allowed = smem;
   }
   const dim3 grid((unsigned)S, (unsigned)p.H, (unsigned)((p.dv + DR_COLS - 1) / DR_COLS));
-  launch_kernel(delta_rule_kernel<RPT>, grid, DR_THREADS, smem, stream, p);
+  launch_kernel(delta_rule_kernel<RPT, CB>, grid, DR_THREADS, smem, stream, p);
   return launch_status("delta_rule");
 }
 
 SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* decay,
                                 const float* a_bias, float* state, const int* q_start, const int* state_slots, float* out,
-                                int S, int H, int dk, int dv, cudaStream_t stream) {
+                                int S, int H, int dk, int dv, int max_q, cudaStream_t stream) {
   SLLM_REQUIRE(S >= 0 && H > 0 && H <= 65535, "delta_rule: bad sizes S=%d H=%d", S, H);
   SLLM_REQUIRE(sllm_delta_rule_supports(dk, dv), "delta_rule: a head of %d key and %d value channels is outside 1..256 keys", dk, dv);
   SLLM_REQUIRE(off_r >= 0 && off_k >= 0 && off_v >= 0 && off_a >= 0 && off_r + H * dk <= ld && off_k + H * dk <= ld &&
@@ -249,11 +293,16 @@ SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k,
   p.proj = proj; p.decay = decay; p.a_bias = a_bias; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
   p.out = out; p.ld = ld; p.off_r = off_r; p.off_k = off_k; p.off_v = off_v; p.off_a = off_a; p.H = H; p.dk = dk; p.dv = dv;
   p.chunk = 1;
-  if (dk <= 16) return launch_delta_rule<2>(p, S, stream);
-  if (dk <= 32) return launch_delta_rule<4>(p, S, stream);
-  if (dk <= 64) return launch_delta_rule<8>(p, S, stream);
-  if (dk <= 128) return launch_delta_rule<16>(p, S, stream);
-  return launch_delta_rule<32>(p, S, stream);
+  p.max_q = max_q;           // the longest portion of the batch (0: not known)
+  // enough (request, head, 64 columns) for every SM: four columns a lane; else one, in four times the CTAs
+  const bool wide = (long)S * H * ((dv + 63) / 64) >= (long)num_sms();
+#define SLLM_DR(RPT_) return wide ? launch_delta_rule<RPT_, 4>(p, S, stream) : launch_delta_rule<RPT_, 1>(p, S, stream)
+  if (dk <= 16) SLLM_DR(2);
+  if (dk <= 32) SLLM_DR(4);
+  if (dk <= 64) SLLM_DR(8);
+  if (dk <= 128) SLLM_DR(16);
+  SLLM_DR(32);
+#undef SLLM_DR
 }
 
 SLLM_EXPORT int sllm_delta_out(const float* o, const float* gain, const float* proj, int ld, int off_g, float eps, void* out,

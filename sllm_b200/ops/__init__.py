@@ -178,7 +178,7 @@ def delta_rule(proj, offs, decay, a_bias, state, step, heads: int, dk: int, dv: 
     out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
     off_r, off_k, off_v, off_a = (int(o) for o in offs)
     call("sllm_delta_rule", _p(proj), ld, off_r, off_k, off_v, off_a, _p(decay), _p(a_bias), _p(state), _p(step.q_start),
-         _p(step.state_slots), _p(out), step.num_seqs, heads, dk, dv, _stream())
+         _p(step.state_slots), _p(out), step.num_seqs, heads, dk, dv, int(step.max_q_len), _stream())
     return out
 
 

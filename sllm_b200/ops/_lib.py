@@ -49,7 +49,7 @@ def _declare(L):
         "sllm_tanh_cols": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p],
         "sllm_delta_rule_supports": [c_int, c_int],
         "sllm_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
-                            c_int, c_int, c_int, c_int, c_void_p],
+                            c_int, c_int, c_int, c_int, c_int, c_void_p],
         "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
         "sllm_latent_write": [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "sllm_head_linear": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
