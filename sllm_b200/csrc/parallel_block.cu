@@ -32,39 +32,6 @@ __global__ void add_sinusoid_kernel(float* __restrict__ stream, const int* __res
   }
 }
 
-// Row t of the stream takes the pending terms (each a stack of `parts` partial sums, float32); then, if
-// rinv is given, rinv[t, g] = 1 / sqrt(mean(stream[t, group g]^2) + eps).  A warp owns a group (warps take
-// groups in turn) and sums it in an order that depends on the group's size only.
-__global__ void add_group_ssq_kernel(float* __restrict__ stream, const float* __restrict__ d0, int parts0, size_t stride0,
-                                     const float* __restrict__ d1, int parts1, size_t stride1,
-                                     float* __restrict__ rinv, int W, int groups, float eps) {
-  pdl_launch_dependents();
-  pdl_wait();
-  const int t = blockIdx.x;
-  float* row = stream + (size_t)t * W;
-  if (d0 != nullptr || d1 != nullptr) {
-    for (int i = threadIdx.x; i < W; i += blockDim.x) {
-      float v = row[i];
-      if (d0 != nullptr)
-        for (int p = 0; p < parts0; ++p) v += d0[p * stride0 + (size_t)t * W + i];
-      if (d1 != nullptr)
-        for (int p = 0; p < parts1; ++p) v += d1[p * stride1 + (size_t)t * W + i];
-      row[i] = v;
-    }
-    __syncthreads();       // the block's own writes are read back below
-  }
-  if (rinv == nullptr) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
-  const int gs = W / groups;
-  for (int g = warp; g < groups; g += nw) {
-    const float* x = row + (size_t)g * gs;
-    float ss = 0.f;
-    for (int i = lane; i < gs; i += 32) ss = fmaf(x[i], x[i], ss);
-    ss = warp_sum(ss);
-    if (lane == 0) rinv[(size_t)t * groups + g] = 1.0f / sqrtf(ss / (float)gs + eps);
-  }
-}
-
 __device__ __forceinline__ float4 pb_load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
 __device__ __forceinline__ float4 pb_load4(const __nv_bfloat16* p) {
   const uint2 raw = *reinterpret_cast<const uint2*>(p);
@@ -79,6 +46,63 @@ __device__ __forceinline__ void pb_store4(__nv_bfloat16* p, float4 v) {
   raw.x = *reinterpret_cast<unsigned*>(&a);
   raw.y = *reinterpret_cast<unsigned*>(&b);
   *reinterpret_cast<uint2*>(p) = raw;
+}
+
+// Row t of the stream takes the pending terms (each a stack of `parts` partial sums, float32); then, if
+// rinv is given, rinv[t, g] = 1 / sqrt(mean(stream[t, group g]^2) + eps).  A warp owns a group (warps take
+// groups in turn) and sums it in an order that depends on the group's size only.  VEC: W and the stacks'
+// strides are multiples of 4 and every pointer is 16-byte aligned; four elements a thread, the partial sums
+// read with independent loads.
+template <bool VEC>
+__global__ void add_group_ssq_kernel(float* __restrict__ stream, const float* __restrict__ d0, int parts0, size_t stride0,
+                                     const float* __restrict__ d1, int parts1, size_t stride1,
+                                     float* __restrict__ rinv, int W, int groups, float eps) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  float* row = stream + (size_t)t * W;
+  if (d0 != nullptr || d1 != nullptr) {
+    if constexpr (VEC) {
+      for (int i = threadIdx.x * 4; i < W; i += blockDim.x * 4) {
+        float4 v = pb_load4(row + i);
+        if (d0 != nullptr) {
+#pragma unroll 8
+          for (int p = 0; p < parts0; ++p) {
+            const float4 x = pb_load4(d0 + p * stride0 + (size_t)t * W + i);
+            v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+          }
+        }
+        if (d1 != nullptr) {
+#pragma unroll 8
+          for (int p = 0; p < parts1; ++p) {
+            const float4 x = pb_load4(d1 + p * stride1 + (size_t)t * W + i);
+            v.x += x.x; v.y += x.y; v.z += x.z; v.w += x.w;
+          }
+        }
+        pb_store4(row + i, v);
+      }
+    } else {
+      for (int i = threadIdx.x; i < W; i += blockDim.x) {
+        float v = row[i];
+        if (d0 != nullptr)
+          for (int p = 0; p < parts0; ++p) v += d0[p * stride0 + (size_t)t * W + i];
+        if (d1 != nullptr)
+          for (int p = 0; p < parts1; ++p) v += d1[p * stride1 + (size_t)t * W + i];
+        row[i] = v;
+      }
+    }
+    __syncthreads();       // the block's own writes are read back below
+  }
+  if (rinv == nullptr) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, nw = blockDim.x >> 5;
+  const int gs = W / groups;
+  for (int g = warp; g < groups; g += nw) {
+    const float* x = row + (size_t)g * gs;
+    float ss = 0.f;
+    for (int i = lane; i < gs; i += 32) ss = fmaf(x[i], x[i], ss);
+    ss = warp_sum(ss);
+    if (lane == 0) rinv[(size_t)t * groups + g] = 1.0f / sqrtf(ss / (float)gs + eps);
+  }
 }
 
 // 1 / sqrt(mean(x[group]^2) + eps) of every group of a row, into dst[groups] (shared memory): warps take groups in
@@ -247,7 +271,11 @@ SLLM_EXPORT int sllm_add_group_ssq(float* stream, const float* d0, int parts0, s
   SLLM_REQUIRE(T >= 0 && W > 0 && groups > 0 && W % groups == 0, "add_group_ssq: %d groups do not divide the width %d", groups, W);
   SLLM_REQUIRE((d0 == nullptr || parts0 >= 1) && (d1 == nullptr || parts1 >= 1), "add_group_ssq: bad parts");
   if (T == 0) return SLLM_OK;
-  launch_kernel(add_group_ssq_kernel, T, 256, 0, stream_, stream, d0, parts0, stride0, d1, parts1, stride1, rinv, W, groups, eps);
+  auto aligned = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+  const bool vec = W % 4 == 0 && stride0 % 4 == 0 && stride1 % 4 == 0 && aligned(stream) && aligned(d0) && aligned(d1);
+  const int threads = W >= 4096 ? 256 : 128;
+  if (vec) launch_kernel(add_group_ssq_kernel<true>, T, threads, 0, stream_, stream, d0, parts0, stride0, d1, parts1, stride1, rinv, W, groups, eps);
+  else launch_kernel(add_group_ssq_kernel<false>, T, threads, 0, stream_, stream, d0, parts0, stride0, d1, parts1, stride1, rinv, W, groups, eps);
   return launch_status("add_group_ssq");
 }
 
