@@ -10,6 +10,7 @@ namespace sllm {
 #define TG_EPI_F32 0
 #define TG_EPI_BF16 1
 #define TG_EPI_SILU 2
+#define TG_EPI_GELU 4      // like TG_EPI_SILU with gelu_tanh(gate + bias) * (up + bias), the bias interleaved like the columns
 #define TG_EPI_RESID 3     // residual[M, N] (float32) += the product (+ bias), in place; see TgExtra
 
 // What an epilogue may do beyond its store, for the RMSNorm that a prompt portion's products take apart
@@ -69,22 +70,31 @@ __device__ __forceinline__ float tg_silu_mul(float g, float u) {
   // silu(g) * u = g * u / (1 + e^-g) (ref/qwen3_5.py:28-29)
   return __fdividef(g * u, 1.0f + __expf(-g));
 }
+constexpr bool tg_gated(int epi) { return epi == TG_EPI_SILU || epi == TG_EPI_GELU; }
+// act(gate) * up of accumulator columns c (gate) and c + 8 (up) of a chunk whose first column is result column n
+template <int EPI>
+__device__ __forceinline__ float tg_act_mul(const uint32_t (&r)[32], int c, int n, const float* __restrict__ bias) {
+  if constexpr (EPI == TG_EPI_GELU) {
+    const float g = __uint_as_float(r[c]) + (bias ? __ldg(bias + n + c) : 0.f), u = __uint_as_float(r[c + 8]) + (bias ? __ldg(bias + n + c + 8) : 0.f);
+    return 0.5f * g * (1.0f + tanhf(0.7978845608028654f * (g + 0.044715f * g * g * g))) * u;
+  } else {
+    return tg_silu_mul(__uint_as_float(r[c]), __uint_as_float(r[c + 8]));
+  }
+}
 
 // r: columns n .. n + 31 of row m of C = A W^T (float32 bits); out is [M, N] (or [M, N/2] for the SiLU form)
 template <int EPI>
 __device__ __forceinline__ void tg_store_chunk(const uint32_t (&r)[32], int m, int n, int N, const float* __restrict__ bias,
                                                void* __restrict__ out) {
-  if constexpr (EPI == TG_EPI_SILU) {
-    // columns alternate 8 gate, 8 up; out[m, (n/16)*8 + i] = silu(gate_i) * up_i
+  if constexpr (tg_gated(EPI)) {
+    // columns alternate 8 gate, 8 up; out[m, (n/16)*8 + i] = act(gate_i) * up_i
     __nv_bfloat16* o = reinterpret_cast<__nv_bfloat16*>(out) + (size_t)m * (N >> 1) + (n >> 1);
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
       if (n + blk * 16 + 15 >= N) break;
       float v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        v[i] = tg_silu_mul(__uint_as_float(r[blk * 16 + i]), __uint_as_float(r[blk * 16 + 8 + i]));
-      }
+      for (int i = 0; i < 8; ++i) v[i] = tg_act_mul<EPI>(r, blk * 16 + i, n, bias);
       if (((N >> 1) & 7) == 0) {               // rows of the result are 16-byte aligned
         *reinterpret_cast<uint4*>(o + blk * 8) = make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7]));
       } else {
@@ -142,13 +152,13 @@ template <int EPI>
 __device__ __forceinline__ void tg_stage_chunk(const uint32_t (&r)[32], unsigned char* stage, int row, int sub, int n, int N,
                                                const float* __restrict__ bias) {
   unsigned char* row_base = stage + row * 128;
-  if constexpr (EPI == TG_EPI_SILU) {
+  if constexpr (tg_gated(EPI)) {
     // 32 columns: 8 gate, 8 up, 8 gate, 8 up -> 16 results = 2 pieces; a box holds 4 such chunks
 #pragma unroll
     for (int blk = 0; blk < 2; ++blk) {
       float v[8];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) v[i] = tg_silu_mul(__uint_as_float(r[blk * 16 + i]), __uint_as_float(r[blk * 16 + 8 + i]));
+      for (int i = 0; i < 8; ++i) v[i] = tg_act_mul<EPI>(r, blk * 16 + i, n, bias);
       tg_put_piece(row_base, row, sub * 2 + blk, make_uint4(pack2(v[0], v[1]), pack2(v[2], v[3]), pack2(v[4], v[5]), pack2(v[6], v[7])));
     }
   } else {

@@ -487,7 +487,7 @@ gemm_pair_wide_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_co
             fence_async_smem();                     // the lanes' writes, before the TMA unit reads them
             __syncwarp();
             if (lane == 0) {
-              tma_store_2d(&map_out, box, EPI == TG_EPI_SILU ? n >> 1 : n, row0);
+              tma_store_2d(&map_out, box, tg_gated(EPI) ? n >> 1 : n, row0);
               bulk_commit();
             }
             staged = true;
@@ -546,7 +546,7 @@ static int launch_tp_wide(const CUtensorMap& ma, const CUtensorMap& mw, const fl
     configured = true;
   }
   // the result leaves through TMA stores where its rows are whole 16-byte pieces; else lane by lane
-  const int out_cols = EPI == TG_EPI_SILU ? N / 2 : N, elem = TgBox<EPI>::ELEM;
+  const int out_cols = tg_gated(EPI) ? N / 2 : N, elem = TgBox<EPI>::ELEM;
   CUtensorMap mo = {};
   int tma_out = 0;
   if (EPI != TG_EPI_RESID && ((size_t)out_cols * elem) % 16 == 0 && ((uintptr_t)out & 15) == 0)
@@ -635,7 +635,7 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
   SLLM_REQUIRE(sllm_gemm_pair_supports(M, N, K), "gemm_pair: sizes M=%d N=%d K=%d (K must be a multiple of 8)", M, N, K);
   SLLM_REQUIRE(((uintptr_t)A & 15) == 0 && ((uintptr_t)W & 15) == 0, "gemm_pair: operands must be 16-byte aligned");
   SLLM_REQUIRE(status != nullptr, "gemm_pair: a status word is required");
-  SLLM_REQUIRE(epilogue != TG_EPI_SILU || N % 16 == 0, "gemm_pair: the SiLU epilogue needs N %% 16 == 0");
+  SLLM_REQUIRE(!tg_gated(epilogue) || N % 16 == 0, "gemm_pair: the gated epilogues need N %% 16 == 0");
   TgExtra extra;
   if (ssq_in != nullptr) {
     SLLM_REQUIRE(parts_in >= 1 && stride_in >= parts_in && width_in >= 1, "gemm_pair: a table of %d partial sums (row stride %d) over width %d",
@@ -684,6 +684,7 @@ SLLM_EXPORT int sllm_gemm_pair(const void* A, const void* W, const float* bias, 
     case TG_EPI_F32: GO(TG_EPI_F32)
     case TG_EPI_BF16: GO(TG_EPI_BF16)
     case TG_EPI_SILU: GO(TG_EPI_SILU)
+    case TG_EPI_GELU: GO(TG_EPI_GELU)
     case TG_EPI_RESID: GO(TG_EPI_RESID)
   }
 #undef GO

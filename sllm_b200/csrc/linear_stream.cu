@@ -32,6 +32,7 @@ constexpr int LS_XSTRIDE = LS_KC + 32;     // bf16 elements: 320 bytes, = 64 mod
 
 #define EPI_STORE 0
 #define EPI_SILU 1
+#define EPI_GELU 2      // the tanh form of GELU in place of SiLU, gate and up each with its bias
 
 constexpr int LS_SSQ_MAX = 608;            // partial sums of squares per token a scaled launch takes (as in linear_ws.cu)
 
@@ -194,19 +195,23 @@ linear_stream_kernel(const __nv_bfloat16* __restrict__ x, const __nv_bfloat16* _
       }
     return;
   }
-  if constexpr (EPI == EPI_SILU) {
+  if constexpr (EPI == EPI_SILU || EPI == EPI_GELU) {
     // rows g (gate i) and g+8 (up i) of this 16-row tile; the output column is (n0/16)*8 + g
     const int col = (n0 >> 4) * 8 + g;
     const int I = N >> 1;
     if (row_b < N) {
+      const float bias_g = (EPI == EPI_GELU && bias) ? bias[row_a] : 0.f, bias_u = (EPI == EPI_GELU && bias) ? bias[row_b] : 0.f;
 #pragma unroll
       for (int j = 0; j < NT; ++j)
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int tok = 8 * j + 2 * t4 + c;
           if (tok < M) {
-            const float gate = acc[j][c], up = acc[j][c + 2];
-            out[(size_t)tok * I + col] = from_f32<OUT>(gate * (1.0f / (1.0f + expf(-gate))) * up);
+            const float gate = acc[j][c] + bias_g, up = acc[j][c + 2] + bias_u;
+            if constexpr (EPI == EPI_GELU)
+              out[(size_t)tok * I + col] = from_f32<OUT>(0.5f * gate * (1.0f + tanhf(0.7978845608028654f * (gate + 0.044715f * gate * gate * gate))) * up);
+            else
+              out[(size_t)tok * I + col] = from_f32<OUT>(gate * (1.0f / (1.0f + expf(-gate))) * up);
           }
         }
     }
@@ -258,7 +263,8 @@ SLLM_EXPORT int sllm_linear_stream_supports(int M, int N, int K) {
 }
 
 // epilogue 0: out[M, N] (+bias) in out_dtype, or with splits > 1 float32 partial[splits, M, N];
-// epilogue 1: out[M, N/2] = silu(gate) * up for rows interleaved in blocks of 8 (splits must be 1).
+// epilogue 1: out[M, N/2] = silu(gate) * up for rows interleaved in blocks of 8 (splits must be 1);
+// epilogue 2: the same with gelu_tanh(gate + bias) * (up + bias), the bias interleaved like the rows.
 SLLM_EXPORT int sllm_linear_stream(const void* x, const void* W, const float* bias, void* out, int out_dtype,
                                    float* partial, int M, int N, int K, int splits, int epilogue,
                                    cudaStream_t stream) {
@@ -266,12 +272,14 @@ SLLM_EXPORT int sllm_linear_stream(const void* x, const void* W, const float* bi
   SLLM_REQUIRE(splits >= 1, "linear_stream: splits=%d", splits);
   SLLM_REQUIRE(splits == 1 || partial != nullptr, "linear_stream: k-splits need scratch");
   SLLM_REQUIRE(epilogue == EPI_STORE || (splits == 1 && N % 16 == 0 && out_dtype == SLLM_BF16),
-               "linear_stream: the SiLU epilogue needs splits=1, N%%16==0 and a bfloat16 result");
+               "linear_stream: the gated epilogues need splits=1, N%%16==0 and a bfloat16 result");
+  SLLM_REQUIRE(epilogue >= EPI_STORE && epilogue <= EPI_GELU, "linear_stream: unknown epilogue %d", epilogue);
   const __nv_bfloat16* xb = (const __nv_bfloat16*)x;
   const __nv_bfloat16* wb = (const __nv_bfloat16*)W;
   const int nt = M <= 8 ? 1 : (M <= 16 ? 2 : (M <= 32 ? 4 : 8));
 #define GO(NT_)                                                                                              \
   if (epilogue == EPI_SILU) return launch_ls<NT_, EPI_SILU, __nv_bfloat16>(xb, wb, bias, out, partial, M, N, K, splits, stream); \
+  if (epilogue == EPI_GELU) return launch_ls<NT_, EPI_GELU, __nv_bfloat16>(xb, wb, bias, out, partial, M, N, K, splits, stream); \
   if (out_dtype == SLLM_BF16) return launch_ls<NT_, EPI_STORE, __nv_bfloat16>(xb, wb, bias, out, partial, M, N, K, splits, stream); \
   return launch_ls<NT_, EPI_STORE, float>(xb, wb, bias, out, partial, M, N, K, splits, stream);
   switch (nt) {

@@ -147,6 +147,27 @@ def act_mul(gu: torch.Tensor, interleave: int, out_dtype: torch.dtype, act: str)
     return out
 
 
+def linear_act_mul(x, w_gate_up, bias, interleave: int, out_dtype, act: str) -> torch.Tensor:
+    """``act(x Wg^T + bg) * (x Wu^T + bu)`` with gate and up rows (and biases) alternating in one matrix in blocks of
+    ``interleave``.  SiLU without biases: `linear_silu_mul`'s kernels.  The tanh form of GELU, bfloat16, blocks of 8: the
+    activation leaves with the product's tile (up to 32 tokens the streaming kernel, prompt portions the CTA-pair
+    product).  Otherwise the product with its bias, then `act_mul`."""
+    if act == "silu" and bias is None:
+        return linear_silu_mul(x, w_gate_up, interleave, out_dtype)
+    if (act == "gelu_tanh" and interleave == 8 and x.is_cuda and x.dtype == torch.bfloat16 and out_dtype == torch.bfloat16
+            and w_gate_up.shape[0] % 16 == 0 and _GATED_FUSED):
+        M, K = x.shape
+        N = w_gate_up.shape[0]
+        if stream_supports(M, N, K):
+            return linear_stream(x, w_gate_up, bias, out_dtype, act=act)
+        if M > TCGEN05_MIN_ROWS and _PAIR_GEMM != "off" and pair_supports(M, N, K):
+            return gemm_pair(x, w_gate_up, bias, out_dtype, act=act)
+    return act_mul(linear(x, w_gate_up, bias, x.dtype), interleave, out_dtype, act)
+
+
+_GATED_FUSED = os.environ.get("SLLM_GATED_FUSED", "1") != "0"      # 0: the product, then the activation kernel
+
+
 def tanh_cols(x: torch.Tensor, col0: int, n: int, out_dtype: torch.dtype) -> torch.Tensor:
     """``tanh(x[:, col0:col0+n])`` of a float32 product, in ``out_dtype``."""
     _chk(x)
@@ -264,11 +285,15 @@ def stream_supports(M: int, N: int, K: int) -> bool:
     return not linear_tc_supports(M, N, K)
 
 
-def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False):
+def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False, act: "str | None" = None):
     """The weight-streaming kernel for at most 64 tokens.  With ``splits`` > 1 the result is
     a float32 stack ``[splits', M, N]`` of partial sums (bias in the first) that the consumer
     adds; with ``silu`` the matrix is gate|up interleaved in blocks of 8 and the result is
-    ``silu(gate) * up`` of width N/2."""
+    ``silu(gate) * up`` of width N/2; with ``act="gelu_tanh"`` it is ``gelu_tanh(gate + bias) * (up + bias)``
+    (the bias interleaved like the rows)."""
+    if act not in (None, "gelu_tanh") or (act and silu):
+        raise KernelError(f"linear_stream: gated epilogue {act!r}")
+    gated = silu or act is not None
     _chk(x, w, bias)
     M, K = x.shape
     N = w.shape[0]
@@ -281,9 +306,9 @@ def linear_stream(x, w, bias, out_dtype, *, splits: int = 1, silu: bool = False)
         partial = torch.empty((real, M, N), dtype=torch.float32, device=x.device)
         out = None
     else:
-        out = torch.empty((M, N // 2 if silu else N), dtype=out_dtype, device=x.device)
+        out = torch.empty((M, N // 2 if gated else N), dtype=out_dtype, device=x.device)
     call("sllm_linear_stream", _p(x), _p(w), _p(bias), _p(out), _dtc(out_dtype), _p(partial), M, N, K,
-         real if real > 1 else 1, 1 if silu else 0, _stream())
+         real if real > 1 else 1, 1 if silu else 2 if act else 0, _stream())
     return partial if real > 1 else out
 
 
@@ -451,7 +476,7 @@ def pair_splits(M: int, N: int, K: int) -> int:
 
 
 def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | None" = None, scale: "RowScale | None" = None,
-              residual=None, next_gain=None, splits: int = 1):
+              residual=None, next_gain=None, splits: int = 1, act: "str | None" = None):
     """The same product and epilogues as `gemm_tcgen05`, by pairs of CTAs on 256 x 256 tiles, on
     256 x 512 tiles (``wide=True``; by default where those fill the GPU at least as well; ``wide=448``, ``384`` or
     ``320``: tiles of that many columns, float32 result or residual epilogue, chosen by `pair_wide_cols` where
@@ -461,10 +486,14 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | 
     into it in place and None is returned; with ``next_gain`` the kernel also writes the next norm's input in the
     owed form and ``(xg, RowScale)`` comes back (the scale's eps left at 0 for the caller to set).
     ``splits`` > 1 (float32 result, no other epilogue): K in that many slices, the result a stack ``[splits', M, N]``
-    of partial sums (bias in the first) for the consumer to add."""
+    of partial sums (bias in the first) for the consumer to add.  ``act="gelu_tanh"``: the gated epilogue
+    ``gelu_tanh(gate + bias) * (up + bias)`` in place of ``silu``'s (rows and bias interleaved in blocks of 8)."""
     _chk(x, w, bias, residual, next_gain)
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError("gemm_pair: bfloat16 operands only")
+    if act not in (None, "gelu_tanh") or (act and silu):
+        raise KernelError(f"gemm_pair: gated epilogue {act!r}")
+    gelu, silu = act is not None, silu or act is not None
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K:
@@ -490,7 +519,7 @@ def gemm_pair(x, w, bias, out_dtype, *, silu: bool = False, wide: "bool | str | 
             xg = torch.empty((M, N), dtype=torch.bfloat16, device=x.device)
             ssq = torch.empty((M, stride), dtype=torch.float32, device=x.device)
     elif silu:
-        epi, out = 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
+        epi, out = 4 if gelu else 2, torch.empty((M, N // 2), dtype=torch.bfloat16, device=x.device)
     elif out_dtype == torch.float32:
         real = int(lib().sllm_gemm_pair_splits(K, int(splits))) if splits > 1 else 1
         epi, out = 0, torch.empty((real, M, N) if real > 1 else (M, N), dtype=torch.float32, device=x.device)

@@ -85,8 +85,9 @@ class Sinusoidal(PositionEncoding):
 @FEED_FORWARDS.register("gated_dense")
 class GatedDense(FeedForward):
     """down(act(gate(x)) * up(x)) with a bias on each of the three products (optional as a set) and ``act`` one of
-    ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) and ``silu``.  gate and up are one matrix, all gate
-    rows first."""
+    ``gelu_tanh`` (0.5 z (1 + tanh(sqrt(2/pi) (z + 0.044715 z^3)))) and ``silu``.  gate and up are one matrix whose rows
+    (and biases) alternate in blocks of 8, so that a tile of the product holds a gate row and its up row together and the
+    activation can be applied where the tile is made (all gate rows first where the size is no multiple of 8)."""
 
     def __init__(self, params, **kw):
         super().__init__(params, **kw)
@@ -96,6 +97,7 @@ class GatedDense(FeedForward):
         self.bias = bool(params.get("bias", True))
         self.names = params.get("names", ("gate", "up", "down"))
         self.bias_suffix = params.get("bias_suffix", "b")
+        self.interleave = 8 if self.inter % 8 == 0 else self.inter
         if self.act not in ops.ACTIVATIONS:
             raise ValueError(f"gated_dense: activation {self.act!r}; known: {sorted(ops.ACTIVATIONS)}")
         self.gate_up = None
@@ -114,15 +116,19 @@ class GatedDense(FeedForward):
     def bind(self, fetch):
         g, u, d = self.names
         b = self.bias_suffix
-        gu_b = self._f32(torch.cat([fetch(f"{g}.{b}").float(), fetch(f"{u}.{b}").float()])) if self.bias else None
-        self.gate_up = Linear(self._matrix(torch.cat([fetch(g), fetch(u)], dim=0)), gu_b)
+        n = self.interleave
+
+        def alternate(a, c):           # blocks of n rows of a, then of c, in turn
+            return torch.stack([a.reshape(self.inter // n, n, *a.shape[1:]), c.reshape(self.inter // n, n, *c.shape[1:])],
+                               dim=1).reshape(2 * self.inter, *a.shape[1:])
+        gu_b = self._f32(alternate(fetch(f"{g}.{b}").float(), fetch(f"{u}.{b}").float())) if self.bias else None
+        self.gate_up = Linear(self._matrix(alternate(fetch(g), fetch(u))), gu_b)
         self.down = Linear(self._matrix(fetch(d)), self._f32(fetch(f"{d}.{b}")) if self.bias else None)
 
     accepts_residual = True
 
     def forward(self, x, step, residual=None):
-        gu = self.gate_up(x, self.dtype)                                     # [T, 2I], biases added by the product
-        act = ops.act_mul(gu, self.inter, self.dtype, self.act)             # [T, I]
+        act = ops.linear_act_mul(x, self.gate_up.weight, self.gate_up.bias, self.interleave, self.dtype, self.act)   # [T, I]
         return self.down.into(act, residual)
 
     def weight_bytes(self):

@@ -228,6 +228,32 @@ def test_gated_activation(dev):
     np.testing.assert_allclose(got, np.tanh(gu[:, 5:16]), rtol=1e-5, atol=1e-6)
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("M,K,I", [(5, 128, 200), (32, 256, 384), (200, 128, 200), (300, 256, 1024), (64, 256, 384), (7, 96, 40)])
+def test_gated_feed_forward_product_with_its_activation_in_the_epilogue(M, K, I):
+    """gelu_tanh(x Wg^T + bg) * (x Wu^T + bu) from the kernels that apply it as the product's tile leaves (few tokens: the
+    streaming kernel; a prompt portion: the CTA-pair product) and from the product followed by the activation kernel,
+    against float64; sizes that take each path, and one that no fused form takes."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(M + K)
+    x = torch.from_numpy(rng.standard_normal((M, K)).astype(np.float32)).cuda().to(torch.bfloat16)
+    wg, wu = (torch.from_numpy((rng.standard_normal((I, K)) * 0.2).astype(np.float32)).cuda().to(torch.bfloat16) for _ in range(2))
+    bg, bu = (torch.from_numpy(rng.standard_normal(I).astype(np.float32)).cuda() for _ in range(2))
+    xd = x.double().cpu().numpy()
+    want = plain.gelu_tanh(xd @ wg.double().cpu().numpy().T + bg.double().cpu().numpy()) * (xd @ wu.double().cpu().numpy().T + bu.double().cpu().numpy())
+    n = 8 if I % 8 == 0 else I
+    alt = lambda a, c: torch.stack([a.reshape(I // n, n, *a.shape[1:]), c.reshape(I // n, n, *c.shape[1:])], dim=1).reshape(2 * I, *a.shape[1:]).contiguous()
+    before = dict(ops.launches)
+    got = ops.linear_act_mul(x, alt(wg, wu), alt(bg, bu), n, torch.bfloat16, "gelu_tanh").float().cpu().numpy()
+    fused = ops.stream_supports(M, 2 * I, K) or (M > 128 and ops.pair_supports(M, 2 * I, K))
+    # (the unfused form rounds gate and up to bfloat16 before the activation: one rounding more, of values up to 16)
+    np.testing.assert_allclose(got, want, rtol=2e-2, atol=3e-2 if fused else 1e-1)
+    assert (ops.launches["own"] + ops.launches["library"] - before["own"] - before["library"] == 1) == bool(fused and n == 8 and (2 * I) % 16 == 0)
+    ops.check_tcgen05_status()
+
+
 @pytest.mark.parametrize("heads,dk", [(1, 64), (3, 16), (2, 40), (1, 130), (80, 16), (2, 6)])
 def test_delta_rule_recurrence_in_portions_and_slots(dev, heads, dk):
     """The recurrence alone: two requests side by side, each cut into portions (down to one token) that continue from

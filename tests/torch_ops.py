@@ -65,6 +65,10 @@ def act_mul(gu, interleave, out_dtype, act):
     return (a * u).reshape(T, I).to(out_dtype)
 
 
+def linear_act_mul(x, w_gate_up, bias, interleave, out_dtype, act):
+    return act_mul(linear(x, w_gate_up, bias, x.dtype), interleave, out_dtype, act)
+
+
 def tanh_cols(x, col0, n, out_dtype):
     return torch.tanh(x[:, col0:col0 + n]).to(out_dtype)
 
@@ -253,6 +257,6 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
+ALL = ["add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
        "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
        "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_", "mark_seen", "penalty_from_seen_"]
