@@ -221,9 +221,9 @@ template <typename TI, typename TO, int ACT, bool VEC>
 __global__ void act_mul_kernel(const TI* __restrict__ gu, TO* __restrict__ out, int I, int interleave) {
   pdl_launch_dependents();
   pdl_wait();
-  const size_t t = blockIdx.y;
+  const size_t t = blockIdx.x;             // (rows on the grid's x: no limit of 65,535)
   constexpr int PER = VEC ? 4 : 1;
-  for (int i = (blockIdx.x * blockDim.x + threadIdx.x) * PER; i < I; i += gridDim.x * blockDim.x * PER) {
+  for (int i = (blockIdx.y * blockDim.x + threadIdx.x) * PER; i < I; i += gridDim.y * blockDim.x * PER) {
     const int b = i / interleave, o = i % interleave;
     const TI* p = gu + t * 2 * I + (size_t)b * 2 * interleave + o;
     if constexpr (VEC) {
@@ -308,8 +308,7 @@ SLLM_EXPORT int sllm_act_mul(const void* gu, int in_dtype, void* out, int out_dt
   SLLM_REQUIRE(act == 0 || act == 1, "act_mul: activation %d is neither 0 (silu) nor 1 (gelu_tanh)", act);
   if (T == 0) return SLLM_OK;
   const int per_block = 256 * 4;
-  const dim3 grid((unsigned)((I + per_block - 1) / per_block > 64 ? 64 : (I + per_block - 1) / per_block), (unsigned)T);
-  SLLM_REQUIRE(T <= 65535, "act_mul: more than 65535 rows in one launch");
+  const dim3 grid((unsigned)T, (unsigned)((I + per_block - 1) / per_block > 64 ? 64 : (I + per_block - 1) / per_block));
   const bool vec = I % 4 == 0 && interleave % 4 == 0 && ((uintptr_t)gu & 15) == 0 && ((uintptr_t)out & 15) == 0;
 #define SLLM_ACT_MUL(TI, TO)                                                                                                       \
   do {                                                                                                                             \
