@@ -52,7 +52,12 @@ ONLY_DELTA = {"architecture": "Rososun", "vocab": 90, "width": 64, "embedding": 
                          {"type": "general_delta", "mixer": {"heads": 2, "dim": 24, "decay_rank": 4}, "mlp": {"kind": "dense", "ff": 96}, "weights_of": 0}]}
 ONLY_LATENT = {"architecture": "Rososun", "vocab": 90, "width": 64, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6, "groups": 8},
                "layers": [{"type": "latent_attention", "mixer": {"heads": 2, "dim": 16, "vdim": 20, "kv_rank": 12, "scale": 0.3}, "mlp": None}]}
-CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 16), "only_delta": (ONLY_DELTA, 4), "only_latent": (ONLY_LATENT, 32)}
+ODD = {               # sizes that are multiples of nothing: no 16-byte row anywhere, so every kernel's plain form runs
+    "architecture": "Rososun", "vocab": 77, "width": 50, "embedding": {"scale": 0.5}, "norm": {"eps": 1e-4, "groups": 5},
+    "layers": [{"type": "general_delta", "mixer": {"heads": 3, "dim": 12, "decay_rank": 5}, "mlp": {"kind": "dense", "ff": 54}},
+               {"type": "latent_attention", "mixer": {"heads": 3, "dim": 10, "vdim": 14, "kv_rank": 21, "scale": 0.4}, "mlp": {"kind": "dense", "ff": 54}}]}
+CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 8), "C": (CONFIG_C, 16), "only_delta": (ONLY_DELTA, 4), "only_latent": (ONLY_LATENT, 32),
+           "odd": (ODD, 16)}
 
 
 def _devices():
@@ -338,7 +343,7 @@ def _requests(vocab, lengths, seed=3):
     return {f"r{i}": rng.integers(0, vocab, n).tolist() for i, n in enumerate(lengths)}
 
 
-@pytest.mark.parametrize("which", ["A", "B", "C", "only_delta", "only_latent"])
+@pytest.mark.parametrize("which", ["A", "B", "C", "only_delta", "only_latent", "odd"])
 def test_every_cutting_against_plain(tmp_path, dev, which):
     """Whole prompts; most of a prompt and the rest token by token; portions of changing size down to two tokens;
     up to four requests at a time, portions beside single tokens.  The pools hold the trace's peak only and freed pages
@@ -422,6 +427,20 @@ def test_keys_far_back_at_page_borders_and_a_long_memory(tmp_path, dev):
         eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=1, poison_freed=True)
         out = traces.replay_engine(tr, eng)
         compare(tr, out, want, dtype, f"far/{dtype}")
+
+
+def test_long_decoding_from_a_short_prompt(tmp_path, dev):
+    """Three tokens of prompt, then 220 tokens one at a time: the recurrent state, the shift state and the latent cache carry
+    everything, across many pages; every step's logits against the plain implementation."""
+    from sllm_b200.engine import Engine, build_model
+    d = make_model(tmp_path, CONFIG_A, seed=41)
+    reqs = _requests(CONFIG_A["vocab"], (223,), seed=42)
+    want = plain_logits(d, reqs)
+    for dtype in dtypes_on(dev):
+        model, _ = build_model(d, dtype, dev)
+        tr = traces.tail_decode(reqs, tail=220)
+        eng = Engine(model, page_size=8, num_pages=tr.max_tokens // 8, max_requests=1)
+        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"long/{dtype}")
 
 
 def test_greedy_generation_through_the_entry_point(tmp_path, dev):
