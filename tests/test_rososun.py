@@ -45,6 +45,8 @@ CONFIG_C = {          # many heads over latents of the sizes the tensor-core att
         {"type": "general_delta", "mixer": {"heads": 3, "dim": 64, "decay_rank": 8}, "mlp": {"kind": "dense", "ff": 256}},
         {"type": "latent_attention", "mixer": {"heads": 32, "dim": 8, "vdim": 8, "kv_rank": 32, "scale": 0.35}, "mlp": None},
         {"type": "latent_attention", "mixer": {"heads": 8, "dim": 24, "vdim": 24, "kv_rank": 16, "scale": 0.2}, "mlp": {"kind": "dense", "ff": 64}},
+        # 24 heads on one latent of 64: even a single decoded token is more rows than the decode form's tile takes
+        {"type": "latent_attention", "mixer": {"heads": 24, "dim": 8, "vdim": 8, "kv_rank": 64, "scale": 0.3}, "mlp": None},
     ],
 }
 ONLY_DELTA = {"architecture": "Rososun", "vocab": 90, "width": 64, "embedding": {"scale": 2.0}, "norm": {"eps": 1e-6, "groups": 2},
