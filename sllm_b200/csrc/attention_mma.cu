@@ -39,6 +39,7 @@ struct AttnParams {
   const int* tile_seq;           // [tiles]
   const int* tile_row0;          // [tiles]
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
+  int block;     // > 0: a query sees only keys of its own block of this many positions (counted from 0)
   float scale_log2;              // scale * log2(e)
 };
 
@@ -85,6 +86,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
   int key_hi = pos0 + (row_hi - 1) / G + 1;      // exclusive: the last row's own position is its last key
   int key_lo = 0;
   if (p.window > 0) key_lo = max(0, pos0 + row0 / G - p.window + 1);
+  if (p.block > 0) key_lo = max(key_lo, (pos0 + row0 / G) / p.block * p.block);
   if (p.num_splits > 1) {
     const int chunk = ((ctx + p.num_splits - 1) / p.num_splits + ATT_BN - 1) / ATT_BN * ATT_BN;
     key_lo = max(key_lo, split * chunk);
@@ -160,6 +162,7 @@ __global__ void __launch_bounds__(AttThreads<DECODE>::value) attention_mma_kerne
       const int pos = pos0 + row / G;
       hi_r[i] = min(pos + 1, key_hi);
       lo_r[i] = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+      if (p.block > 0) lo_r[i] = max(lo_r[i], pos / p.block * p.block);
     } else {
       hi_r[i] = 0;
       lo_r[i] = 1;                                // empty
@@ -413,7 +416,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
                                    float* part_lse, const int* block_tables, int max_pages, const int* q_start,
                                    const int* ctx_len, const int* tile_seq, const int* tile_row0, int tiles,
                                    int decode, int num_splits, int total_tokens, int nq, int nkv, int hd,
-                                   int page_size, float scale, int window, cudaStream_t stream) {
+                                   int page_size, float scale, int window, int block, cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_mma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_mma_supports(hd), "attention_mma: head_dim=%d is not one of 16, 32, 64, 128", hd);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0 && tiles >= 0 && total_tokens >= 0, "attention_mma: bad sizes");
@@ -424,7 +427,7 @@ SLLM_EXPORT int sllm_attention_mma(const void* q, const void* k_cache, const voi
   p.q = (const __nv_bfloat16*)q; p.k_cache = (const __nv_bfloat16*)k_cache; p.v_cache = (const __nv_bfloat16*)v_cache;
   p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse; p.block_tables = block_tables;
   p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
-  p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
+  p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = block;
   p.num_splits = num_splits; p.total_tokens = total_tokens;
   p.scale_log2 = scale * 1.4426950408889634f;
 #define DISPATCH(HD_)                                                             \

@@ -4,7 +4,8 @@
 // single decoded tokens are the same work, so a position's result cannot depend on
 // how the batch was cut.
 //
-//   s_j = (q . k_j) * scale for keys j <= pos (and j > pos - window), softmax with the
+//   s_j = (q . k_j) * scale for keys j <= pos (and j > pos - window; and, with `chunk`, j in pos's own block of
+//   `chunk` positions counted from 0), softmax with the
 //   maximum subtracted, o = sum p_j v_j   (ref/qwen3_5.py:373-390; one row:
 //   ref/incremental.py:75-87; kernels/cuda/kernels.cu:957-1025 for one CTA per head).
 //   Query head h reads kv head h / (nq / nkv) (ref/standard.py:65-68).
@@ -27,7 +28,7 @@ __global__ void __launch_bounds__(ATT_WARPS * 32)
 attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, const TC* __restrict__ v_cache,
                       const int* __restrict__ block_tables, int max_pages, const int* __restrict__ positions,
                       const int* __restrict__ seq_of_token, int nq, int nkv, int hd, int page_size, float scale,
-                      int window, TQ* __restrict__ out) {
+                      int window, int chunk, TQ* __restrict__ out) {
   __shared__ float qs[ATT_MAX_HD];
   __shared__ float acc_s[ATT_WARPS][ATT_MAX_HD];
   __shared__ float m_s[ATT_WARPS], l_s[ATT_WARPS];
@@ -37,7 +38,8 @@ attention_simt_kernel(const TQ* __restrict__ q, const TC* __restrict__ k_cache, 
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int pos = positions[t];
   const int* bt = block_tables + (size_t)seq_of_token[t] * max_pages;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (chunk > 0) lo = max(lo, pos / chunk * chunk);
 
   for (int d = threadIdx.x; d < hd; d += blockDim.x) qs[d] = to_f32(q[((size_t)t * nq + h) * hd + d]);
   __syncthreads();
@@ -99,7 +101,7 @@ using namespace sllm;
 SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const void* v_cache, int dtype,
                                     const int* block_tables, int max_pages, const int* positions,
                                     const int* seq_of_token, int T, int nq, int nkv, int hd, int page_size,
-                                    float scale, int window, void* out, cudaStream_t stream) {
+                                    float scale, int window, int chunk, void* out, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && nq % nkv == 0, "attention: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(hd > 0 && hd <= ATT_MAX_HD, "attention: head_dim=%d is outside 1..%d", hd, ATT_MAX_HD);
   SLLM_REQUIRE(page_size > 0 && max_pages > 0, "attention: bad page_size=%d max_pages=%d", page_size, max_pages);
@@ -109,11 +111,11 @@ SLLM_EXPORT int sllm_attention_simt(const void* q, const void* k_cache, const vo
   if (dtype == SLLM_F32)
     launch_kernel(attention_simt_kernel<float, float>, grid, ATT_WARPS * 32, 0, stream,
         (const float*)q, (const float*)k_cache, (const float*)v_cache, block_tables, max_pages, positions,
-        seq_of_token, nq, nkv, hd, page_size, scale, window, (float*)out);
+        seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, (float*)out);
   else if (dtype == SLLM_BF16)
     launch_kernel(attention_simt_kernel<__nv_bfloat16, __nv_bfloat16>, grid, ATT_WARPS * 32, 0, stream,
         (const __nv_bfloat16*)q, (const __nv_bfloat16*)k_cache, (const __nv_bfloat16*)v_cache, block_tables,
-        max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, (__nv_bfloat16*)out);
+        max_pages, positions, seq_of_token, nq, nkv, hd, page_size, scale, window, chunk, (__nv_bfloat16*)out);
   else
     SLLM_REQUIRE(false, "attention: unknown dtype %d", dtype);
   return launch_status("attention_simt");

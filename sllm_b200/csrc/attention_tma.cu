@@ -47,6 +47,7 @@ struct AttnTmaParams {
   const int* tile_row0;          // [tiles]
   int* status;
   int max_pages, page_size, nq, nkv, window, num_splits, total_tokens;
+  int block;     // > 0: a query sees only keys of its own block of this many positions (counted from 0)
   int page_runs;                 // the run maps are valid: a tile of pages with consecutive ids is fetched as one box
   float scale_log2;
 };
@@ -112,6 +113,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
   int key_hi = pos0 + (row_hi - 1) / G + 1;
   int key_lo = 0;
   if (p.window > 0) key_lo = max(0, pos0 + row0 / G - p.window + 1);
+  if (p.block > 0) key_lo = max(key_lo, (pos0 + row0 / G) / p.block * p.block);
   if (p.num_splits > 1) {
     const int chunk = ((ctx + p.num_splits - 1) / p.num_splits + TA_BN - 1) / TA_BN * TA_BN;
     key_lo = max(key_lo, split * chunk);
@@ -215,6 +217,7 @@ attention_tma_decode_kernel(const __grid_constant__ CUtensorMap map_k, const __g
         const int pos = pos0 + row / G;
         hi_r[i] = min(pos + 1, key_hi);
         lo_r[i] = p.window > 0 ? max(key_lo, pos - p.window + 1) : key_lo;
+        if (p.block > 0) lo_r[i] = max(lo_r[i], pos / p.block * p.block);
       } else {
         hi_r[i] = 0;
         lo_r[i] = 1;
@@ -568,7 +571,7 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
                                           void* out, float* part_o, float* part_lse, const int* block_tables,
                                           int max_pages, const int* q_start, const int* ctx_len, const int* tile_seq,
                                           const int* tile_row0, int tiles, int num_splits, int total_tokens, int nq,
-                                          int nkv, int hd, int page_size, float scale, int window, int* status,
+                                          int nkv, int hd, int page_size, float scale, int window, int block, int* status,
                                           cudaStream_t stream) {
   SLLM_REQUIRE(nq > 0 && nkv > 0 && nq % nkv == 0, "attention_tma: bad head counts nq=%d nkv=%d", nq, nkv);
   SLLM_REQUIRE(sllm_attention_tma_supports(hd, page_size), "attention_tma: head_dim=%d page_size=%d not taken", hd, page_size);
@@ -593,7 +596,7 @@ SLLM_EXPORT int sllm_attention_tma_decode(const void* q, const void* k_cache, co
   p.page_runs = runs ? 1 : 0;
   p.q = (const __nv_bfloat16*)q; p.out = (__nv_bfloat16*)out; p.part_o = part_o; p.part_lse = part_lse;
   p.block_tables = block_tables; p.q_start = q_start; p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0;
-  p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window;
+  p.status = status; p.max_pages = max_pages; p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.window = window; p.block = block;
   p.num_splits = num_splits; p.total_tokens = total_tokens; p.scale_log2 = scale * 1.4426950408889634f;
 
   return hd == 128 ? launch_ta<128>(mk, mv, rk, rv, p, tiles, stream) : launch_ta<64>(mk, mv, rk, rv, p, tiles, stream);

@@ -20,6 +20,16 @@
 // A portion of a prompt and a single decoded token run through the same kernel, from the state slot and back
 // into it.
 //
+// Two more recurrences walk the same way, because each is the line above with other vectors in the five places
+// (`mode`; only what the loader warps prepare differs):
+//   the gated delta rule (mode 1):  S <- g S;  w = beta (v - S^T k^);  S <- S + k^ w^T;  o = S^T q^
+//       with k^ = k / sqrt(sum(k^2) + 1e-6), q^ likewise times r_scale, beta = sigmoid(b), g = exp(-exp(A) softplus(a + dt))
+//       one number per head.  In terms of the state before the token: S <- g S - (beta g k^)(k^^T S) + k^ (beta v)^T,
+//       so u = k = k^, d = g on every row, a*u = beta g k^, v = beta v, r = q^.  Several value heads may share one
+//       query/key head (head h reads key head h / hdiv).
+//   gated linear attention (mode 2):  S <- diag(alpha) S + k v^T;  o = S^T (q r_scale),  alpha = sigmoid(z)^(1/tau) per key
+//       channel: u = a*u = 0, d = alpha.
+//
 // A second kernel finishes the mixer's output: each head's o over its root mean square, times a gain,
 // times sigmoid(gate logit), in the compute dtype.
 #include "common.cuh"
@@ -41,6 +51,13 @@ struct DeltaParams {
   const int* state_slots;  // [S]
   float* out;              // [T, H*dv]
   int ld, off_r, off_k, off_v, off_a, H, dk, dv, chunk, max_q;
+  // modes 1 and 2 (see the head of the file)
+  int mode, hdiv;          // hdiv: value heads per query/key head
+  const float* gates;      // mode 1: [T, ldg] with beta logits at off_b + h and decay logits at off_dt + h
+  int ldg, off_b, off_dt;
+  const float* a_log;      // mode 1: [H]
+  const float* dt_bias;    // mode 1: [H]
+  float r_scale, inv_tau;  // the read-out's factor; mode 2: 1 / tau
 };
 
 // RPT: rows of a column per lane (dk <= 8 * RPT = DKP, the padded key size).
@@ -77,14 +94,15 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
       const bool tok = tt < nt;
       const float* row = p.proj + (size_t)(t0 + (tok ? tt : 0)) * p.ld;
       const float* dec = p.decay + (size_t)(t0 + (tok ? tt : 0)) * p.H * dk + h * dk;
+      const int kh = h / p.hdiv;
 #pragma unroll
       for (int m = 0; m < PER_LANE; ++m) {
         const int i = lane + 32 * m;
         const bool in = tok && i < dk;
-        k[q][m] = in ? __ldg(row + p.off_k + h * dk + i) : 0.f;
-        a[q][m] = in ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
-        d[q][m] = in ? __ldg(dec + i) : 0.f;
-        r[q][m] = in ? __ldg(row + p.off_r + h * dk + i) : 0.f;
+        k[q][m] = in ? __ldg(row + p.off_k + kh * dk + i) : 0.f;
+        a[q][m] = (in && p.mode == 0) ? __ldg(row + p.off_a + h * dk + i) + __ldg(p.a_bias + h * dk + i) : 0.f;
+        d[q][m] = (in && p.mode != 1) ? __ldg(dec + i) : 0.f;
+        r[q][m] = in ? __ldg(row + p.off_r + kh * dk + i) : 0.f;
       }
 #pragma unroll
       for (int m = 0; m < VPL; ++m) {
@@ -101,22 +119,63 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
       for (int m = 0; m < PER_LANE; ++m) ss = fmaf(k[q][m], k[q][m], ss);
       ss = warp_sum(ss);
       const float inv = 1.0f / sqrtf(ss + 1e-6f);
+      float vmul = 1.f;
+      if (p.mode == 0) {
 #pragma unroll
-      for (int m = 0; m < PER_LANE; ++m) {
-        const int i = lane + 32 * m;
-        if (i < DKP) {
-          const bool in = i < dk;
-          const float u = k[q][m] * inv;
-          s_k[tt * DKP + i] = k[q][m];
-          s_u[tt * DKP + i] = u;
-          s_au[tt * DKP + i] = in ? sigmoidf_(a[q][m]) * u : 0.f;
-          s_d[tt * DKP + i] = in ? expf(c_decay * sigmoidf_(d[q][m])) : 0.f;
-          s_r[tt * DKP + i] = r[q][m];
+        for (int m = 0; m < PER_LANE; ++m) {
+          const int i = lane + 32 * m;
+          if (i < DKP) {
+            const bool in = i < dk;
+            const float u = k[q][m] * inv;
+            s_k[tt * DKP + i] = k[q][m];
+            s_u[tt * DKP + i] = u;
+            s_au[tt * DKP + i] = in ? sigmoidf_(a[q][m]) * u : 0.f;
+            s_d[tt * DKP + i] = in ? expf(c_decay * sigmoidf_(d[q][m])) : 0.f;
+            s_r[tt * DKP + i] = r[q][m];
+          }
+        }
+      } else if (p.mode == 1) {
+        float sr = 0.f;
+#pragma unroll
+        for (int m = 0; m < PER_LANE; ++m) sr = fmaf(r[q][m], r[q][m], sr);
+        sr = warp_sum(sr);
+        const float rinv = p.r_scale / sqrtf(sr + 1e-6f);
+        const float* gr = p.gates + (size_t)(t0 + tt) * p.ldg;
+        const float beta = sigmoidf_(__ldg(gr + p.off_b + h));
+        const float x = __ldg(gr + p.off_dt + h) + __ldg(p.dt_bias + h);
+        const float g = expf(-expf(__ldg(p.a_log + h)) * (fmaxf(x, 0.f) + log1pf(expf(-fabsf(x)))));
+        vmul = beta;
+#pragma unroll
+        for (int m = 0; m < PER_LANE; ++m) {
+          const int i = lane + 32 * m;
+          if (i < DKP) {
+            const bool in = i < dk;
+            const float u = k[q][m] * inv;
+            s_k[tt * DKP + i] = u;
+            s_u[tt * DKP + i] = u;
+            s_au[tt * DKP + i] = beta * g * u;
+            s_d[tt * DKP + i] = in ? g : 0.f;
+            s_r[tt * DKP + i] = r[q][m] * rinv;
+          }
+        }
+      } else {
+#pragma unroll
+        for (int m = 0; m < PER_LANE; ++m) {
+          const int i = lane + 32 * m;
+          if (i < DKP) {
+            const bool in = i < dk;
+            const float z = d[q][m];
+            s_k[tt * DKP + i] = k[q][m];
+            s_u[tt * DKP + i] = 0.f;
+            s_au[tt * DKP + i] = 0.f;
+            s_d[tt * DKP + i] = in ? expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * p.inv_tau) : 0.f;
+            s_r[tt * DKP + i] = r[q][m] * p.r_scale;
+          }
         }
       }
 #pragma unroll
       for (int m = 0; m < VPL; ++m)
-        if (lane + 32 * m < COLS) s_v[tt * COLS + lane + 32 * m] = v[q][m];
+        if (lane + 32 * m < COLS) s_v[tt * COLS + lane + 32 * m] = v[q][m] * vmul;
     }
   };
 
@@ -232,10 +291,11 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
   }
 }
 
-// out[t, h*dv + j] = o[t, h, j] / sqrt(mean_j(o[t, h, :]^2) + eps) * gain[h*dv + j] * sigmoid(gate[t, h*dv + j]); a warp per (t, h).
+// out[t, h*dv + j] = o[t, h, j] / sqrt(mean_j(o[t, h, :]^2) + eps) * gain[h*dv + j] * act(gate[t, h*dv + j]), act the sigmoid
+// (gate_act 0) or z * sigmoid(z) (gate_act 1); a warp per (t, h).
 template <typename TO>
 __global__ void delta_out_kernel(const float* __restrict__ o, const float* __restrict__ gain, const float* __restrict__ proj,
-                                 int ld, int off_g, float eps, TO* __restrict__ out, int rows, int H, int dv) {
+                                 int ld, int off_g, float eps, TO* __restrict__ out, int rows, int H, int dv, int gate_act) {
   pdl_launch_dependents();
   pdl_wait();
   const int lane = threadIdx.x & 31;
@@ -248,8 +308,10 @@ __global__ void delta_out_kernel(const float* __restrict__ o, const float* __res
   ss = warp_sum(ss);
   const float inv = 1.0f / sqrtf(ss / (float)dv + eps);
   const float* g = proj + (size_t)t * ld + off_g + h * dv;
-  for (int j = lane; j < dv; j += 32)
-    out[(size_t)row * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * sigmoidf_(g[j]));
+  for (int j = lane; j < dv; j += 32) {
+    const float gate = gate_act == 1 ? g[j] * sigmoidf_(g[j]) : sigmoidf_(g[j]);
+    out[(size_t)row * dv + j] = from_f32<TO>(x[j] * inv * gain[h * dv + j] * gate);
+  }
 }
 
 }  // namespace sllm
@@ -281,6 +343,8 @@ static int launch_delta_rule(DeltaParams p, int S, cudaStream_t stream) {
   return launch_status("delta_rule");
 }
 
+static int dispatch_delta_rule(DeltaParams p, int S, cudaStream_t stream);
+
 SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k, int off_v, int off_a, const float* decay,
                                 const float* a_bias, float* state, const int* q_start, const int* state_slots, float* out,
                                 int S, int H, int dk, int dv, int max_q, cudaStream_t stream) {
@@ -294,8 +358,15 @@ SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k,
   p.out = out; p.ld = ld; p.off_r = off_r; p.off_k = off_k; p.off_v = off_v; p.off_a = off_a; p.H = H; p.dk = dk; p.dv = dv;
   p.chunk = 1;
   p.max_q = max_q;           // the longest portion of the batch (0: not known)
+  p.mode = 0; p.hdiv = 1; p.gates = nullptr; p.ldg = p.off_b = p.off_dt = 0; p.a_log = p.dt_bias = nullptr;
+  p.r_scale = 1.f; p.inv_tau = 1.f;
+  return dispatch_delta_rule(p, S, stream);
+}
+
+static int dispatch_delta_rule(DeltaParams p, int S, cudaStream_t stream) {
+  const int dk = p.dk, dv = p.dv;
   // enough (request, head, 64 columns) for every SM: four columns a lane; else one, in four times the CTAs
-  const bool wide = (long)S * H * ((dv + 63) / 64) >= (long)num_sms();
+  const bool wide = (long)S * p.H * ((dv + 63) / 64) >= (long)num_sms();
 #define SLLM_DR(RPT_) return wide ? launch_delta_rule<RPT_, 4>(p, S, stream) : launch_delta_rule<RPT_, 1>(p, S, stream)
   if (dk <= 16) SLLM_DR(2);
   if (dk <= 32) SLLM_DR(4);
@@ -305,17 +376,56 @@ SLLM_EXPORT int sllm_delta_rule(const float* proj, int ld, int off_r, int off_k,
 #undef SLLM_DR
 }
 
+// The gated delta rule over conv'd, activated q | k | v columns of `qkv` [T, ld] (query/key heads Hk, value heads H) with
+// one beta logit and one decay logit per head in `gates` [T, ldg].
+SLLM_EXPORT int sllm_gated_delta_rule(const float* qkv, int ld, int off_q, int off_k, int off_v, const float* gates, int ldg,
+                                      int off_b, int off_dt, const float* a_log, const float* dt_bias, float* state,
+                                      const int* q_start, const int* state_slots, float* out, int S, int H, int Hk, int dk, int dv,
+                                      float q_scale, int max_q, cudaStream_t stream) {
+  SLLM_REQUIRE(S >= 0 && H > 0 && H <= 65535 && Hk > 0 && H % Hk == 0, "gated_delta_rule: bad sizes S=%d H=%d Hk=%d", S, H, Hk);
+  SLLM_REQUIRE(sllm_delta_rule_supports(dk, dv), "gated_delta_rule: a head of %d key and %d value channels is outside 1..256 keys", dk, dv);
+  SLLM_REQUIRE(off_q >= 0 && off_k >= 0 && off_v >= 0 && off_q + Hk * dk <= ld && off_k + Hk * dk <= ld && off_v + H * dv <= ld,
+               "gated_delta_rule: columns outside the product's %d", ld);
+  SLLM_REQUIRE(off_b >= 0 && off_dt >= 0 && off_b + H <= ldg && off_dt + H <= ldg, "gated_delta_rule: gate columns outside %d", ldg);
+  if (S == 0) return SLLM_OK;
+  DeltaParams p;
+  p.proj = qkv; p.decay = qkv; p.a_bias = nullptr; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
+  p.out = out; p.ld = ld; p.off_r = off_q; p.off_k = off_k; p.off_v = off_v; p.off_a = 0; p.H = H; p.dk = dk; p.dv = dv;
+  p.chunk = 1; p.max_q = max_q;
+  p.mode = 1; p.hdiv = H / Hk; p.gates = gates; p.ldg = ldg; p.off_b = off_b; p.off_dt = off_dt; p.a_log = a_log; p.dt_bias = dt_bias;
+  p.r_scale = q_scale; p.inv_tau = 1.f;
+  return dispatch_delta_rule(p, S, stream);
+}
+
+// Gated linear attention over q | k | v columns of `proj` [T, ld] with decay logits `z` [T, H*dk]: alpha = sigmoid(z)^(inv_tau).
+SLLM_EXPORT int sllm_gated_linear_attention(const float* proj, int ld, int off_q, int off_k, int off_v, const float* z,
+                                            float* state, const int* q_start, const int* state_slots, float* out, int S, int H,
+                                            int dk, int dv, float q_scale, float inv_tau, int max_q, cudaStream_t stream) {
+  SLLM_REQUIRE(S >= 0 && H > 0 && H <= 65535, "gated_linear_attention: bad sizes S=%d H=%d", S, H);
+  SLLM_REQUIRE(sllm_delta_rule_supports(dk, dv), "gated_linear_attention: a head of %d key and %d value channels is outside 1..256 keys", dk, dv);
+  SLLM_REQUIRE(off_q >= 0 && off_k >= 0 && off_v >= 0 && off_q + H * dk <= ld && off_k + H * dk <= ld && off_v + H * dv <= ld,
+               "gated_linear_attention: columns outside the product's %d", ld);
+  if (S == 0) return SLLM_OK;
+  DeltaParams p;
+  p.proj = proj; p.decay = z; p.a_bias = nullptr; p.state = state; p.q_start = q_start; p.state_slots = state_slots;
+  p.out = out; p.ld = ld; p.off_r = off_q; p.off_k = off_k; p.off_v = off_v; p.off_a = 0; p.H = H; p.dk = dk; p.dv = dv;
+  p.chunk = 1; p.max_q = max_q;
+  p.mode = 2; p.hdiv = 1; p.gates = nullptr; p.ldg = p.off_b = p.off_dt = 0; p.a_log = p.dt_bias = nullptr;
+  p.r_scale = q_scale; p.inv_tau = inv_tau;
+  return dispatch_delta_rule(p, S, stream);
+}
+
 SLLM_EXPORT int sllm_delta_out(const float* o, const float* gain, const float* proj, int ld, int off_g, float eps, void* out,
-                               int out_dtype, int T, int H, int dv, cudaStream_t stream) {
+                               int out_dtype, int T, int H, int dv, int gate_act, cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && H > 0 && dv > 0 && off_g >= 0 && off_g + H * dv <= ld, "delta_out: bad sizes T=%d H=%d dv=%d", T, H, dv);
   if (T == 0) return SLLM_OK;
   const long rows = (long)T * H;
   const int blocks = (int)((rows + 7) / 8);
   if (out_dtype == SLLM_F32)
-    launch_kernel(delta_out_kernel<float>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, (int)rows, H, dv);
+    launch_kernel(delta_out_kernel<float>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (float*)out, (int)rows, H, dv, gate_act);
   else if (out_dtype == SLLM_BF16)
     launch_kernel(delta_out_kernel<__nv_bfloat16>, blocks, 256, 0, stream, o, gain, proj, ld, off_g, eps, (__nv_bfloat16*)out,
-                  (int)rows, H, dv);
+                  (int)rows, H, dv, gate_act);
   else
     SLLM_REQUIRE(false, "delta_out: unknown dtype %d", out_dtype);
   return launch_status("delta_out");

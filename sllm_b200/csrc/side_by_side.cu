@@ -1,0 +1,180 @@
+// Kernels of a layer that runs two mixers side by side: softmax attention with normed queries and keys
+// next to a recurrence behind short convolutions, and the normed mean of their outputs.
+//
+//   qk_norm_rope_kv_write   q | k | v columns of a float32 product: each query and key head over its root mean
+//                           square times a gain shared by the heads, then rotated (the first `rot` channels, channel i
+//                           with i + rot/2, by the table's cos and sin of the token's position); values as they are.
+//                           Queries leave in the compute dtype, keys and values go to their token's place in the pages.
+//                           Key and value sizes may differ: the cache's head is D >= both, the rest is zeros.
+//   short_conv_silu         y[t, c] = silu(sum_j w[c, taps-1-j] x[t-j, c]) over a request's own tokens; the taps-1 inputs
+//                           before a portion come from the request's state row, zeros before the sequence starts.
+//   short_conv_state        the state row receives the portion's last taps-1 inputs (older ones move up).
+//   norm_mean_add           stream += (a / rms(a) * ga + b / rms(b) * gb) / 2.
+//
+// All arithmetic is float32.
+#include "common.cuh"
+
+namespace sllm {
+
+__device__ __forceinline__ float sbs_silu(float z) { return z / (1.0f + expf(-z)); }
+
+template <typename TC>
+__global__ void __launch_bounds__(128)
+qk_norm_rope_kv_write_kernel(const float* __restrict__ qkv, int ld, const float* __restrict__ q_gain,
+                             const float* __restrict__ k_gain, float eps, const int* __restrict__ positions,
+                             const float* __restrict__ table, int rot, int max_pos, int nq, int nkv, int dim, int vdim, int D,
+                             const int* __restrict__ slot_mapping, int page_size, int num_pages, TC* __restrict__ k_cache,
+                             TC* __restrict__ v_cache, TC* __restrict__ q_out, int T) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31;
+  const int heads = nq + 2 * nkv;
+  const long item = (long)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (item >= (long)T * heads) return;
+  const int t = (int)(item / heads), head = (int)(item % heads);
+  const float* row = qkv + (size_t)t * ld;
+  TC* dst;
+  if (head < nq) {
+    dst = q_out + ((size_t)t * nq + head) * D;
+  } else {
+    if (slot_mapping == nullptr) return;
+    const int slot = slot_mapping[t];
+    if (slot < 0 || slot / page_size >= num_pages) return;          // a row that writes nothing (padding, a borrowed cache)
+    const bool is_k = head < nq + nkv;
+    const int kvh = is_k ? head - nq : head - nq - nkv;
+    dst = (is_k ? k_cache : v_cache) + (((size_t)(slot / page_size) * nkv + kvh) * page_size + slot % page_size) * D;
+  }
+  if (head >= nq + nkv) {                                            // a value head: copied, zeros beyond vdim
+    const float* x = row + (size_t)(nq + nkv) * dim + (size_t)(head - nq - nkv) * vdim;
+    for (int d = lane; d < D; d += 32) dst[d] = from_f32<TC>(d < vdim ? x[d] : 0.f);
+    return;
+  }
+  const float* x = row + (size_t)head * dim;
+  const float* gain = head < nq ? q_gain : k_gain;
+  float ss = 0.f;
+  for (int d = lane; d < dim; d += 32) ss = fmaf(x[d], x[d], ss);
+  ss = warp_sum(ss);
+  const float inv = 1.0f / sqrtf(ss / (float)dim + eps);
+  const int half = rot / 2;
+  if (rot > 0) {
+    int pos = positions[t];
+    pos = pos < 0 ? 0 : (pos >= max_pos ? max_pos - 1 : pos);
+    const float* cs = table + (size_t)pos * rot;                    // cos[half] then sin[half]
+    for (int j = lane; j < half; j += 32) {
+      const float u = x[j] * inv * gain[j], v = x[j + half] * inv * gain[j + half];
+      const float c = cs[j], sn = cs[half + j];
+      dst[j] = from_f32<TC>(u * c - v * sn);
+      dst[j + half] = from_f32<TC>(v * c + u * sn);
+    }
+  }
+  for (int d = rot + lane; d < D; d += 32) dst[d] = from_f32<TC>(d < dim ? x[d] * inv * gain[d] : 0.f);
+}
+
+// grid (T, ceil(C / 256)): a thread per (token, channel)
+__global__ void __launch_bounds__(256)
+short_conv_silu_kernel(const float* __restrict__ x, int ld, int off, const float* __restrict__ w, int taps,
+                       const float* __restrict__ state, const int* __restrict__ seq_of_token, const int* __restrict__ q_start,
+                       const int* __restrict__ state_slots, float* __restrict__ out, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int seq = seq_of_token[t];
+  const int first = q_start[seq];
+  const float* st = state + ((size_t)state_slots[seq] * C + c) * (taps - 1);
+  const float* wc = w + (size_t)c * taps;
+  float acc = 0.f;
+  for (int j = taps - 1; j >= 0; --j) {                 // oldest input first: one order whatever the cut
+    const int src = t - j;
+    const float v = src >= first ? x[(size_t)src * ld + off + c] : st[taps - 1 - (first - src)];
+    acc = fmaf(wc[taps - 1 - j], v, acc);
+  }
+  out[(size_t)t * C + c] = sbs_silu(acc);
+}
+
+// grid (S, ceil(C / 256)): a thread per (request, channel) rewrites its state row in ascending order
+__global__ void __launch_bounds__(256)
+short_conv_state_kernel(const float* __restrict__ x, int ld, int off, int taps, float* __restrict__ state,
+                        const int* __restrict__ q_start, const int* __restrict__ state_slots, int C) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seq = blockIdx.x, c = blockIdx.y * blockDim.x + threadIdx.x;
+  if (c >= C) return;
+  const int first = q_start[seq], n = q_start[seq + 1] - first, keep = taps - 1;
+  float* st = state + ((size_t)state_slots[seq] * C + c) * keep;
+  for (int i = 0; i < keep; ++i) {
+    const int idx = n - keep + i;                       // which of the portion's tokens, negative: still the old state's
+    st[i] = idx >= 0 ? x[(size_t)(first + idx) * ld + off + c] : st[i + n];
+  }
+}
+
+// a CTA per token
+__global__ void __launch_bounds__(256)
+norm_mean_add_kernel(float* __restrict__ stream, const float* __restrict__ a, const float* __restrict__ ga,
+                     const float* __restrict__ b, const float* __restrict__ gb, float eps, int W) {
+  __shared__ float red[33];
+  pdl_launch_dependents();
+  pdl_wait();
+  const size_t base = (size_t)blockIdx.x * W;
+  float sa = 0.f, sb = 0.f;
+  for (int i = threadIdx.x; i < W; i += blockDim.x) {
+    const float va = a[base + i], vb = b[base + i];
+    sa = fmaf(va, va, sa);
+    sb = fmaf(vb, vb, sb);
+  }
+  sa = block_sum(sa, red);
+  sb = block_sum(sb, red);
+  const float ia = 1.0f / sqrtf(sa / (float)W + eps), ib = 1.0f / sqrtf(sb / (float)W + eps);
+  for (int i = threadIdx.x; i < W; i += blockDim.x)
+    stream[base + i] += 0.5f * (a[base + i] * ia * ga[i] + b[base + i] * ib * gb[i]);
+}
+
+}  // namespace sllm
+
+using namespace sllm;
+
+SLLM_EXPORT int sllm_qk_norm_rope_kv_write(const float* qkv, int ld, const float* q_gain, const float* k_gain, float eps,
+                                           const int* positions, const float* table, int rot, int max_pos, int nq, int nkv,
+                                           int dim, int vdim, int D, const int* slot_mapping, int page_size, int num_pages,
+                                           void* k_cache, void* v_cache, void* q_out, int cache_dtype, int T, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && nq > 0 && nkv > 0 && dim > 0 && vdim > 0, "qk_norm_rope: bad sizes T=%d nq=%d nkv=%d dim=%d vdim=%d", T, nq, nkv, dim, vdim);
+  SLLM_REQUIRE(D >= dim && D >= vdim, "qk_norm_rope: the cache's head of %d is smaller than a key of %d or a value of %d", D, dim, vdim);
+  SLLM_REQUIRE(ld >= (nq + nkv) * dim + nkv * vdim, "qk_norm_rope: the product's %d columns are fewer than q|k|v", ld);
+  SLLM_REQUIRE(rot >= 0 && rot <= dim && rot % 2 == 0, "qk_norm_rope: rotary_dim=%d must be even and <= %d", rot, dim);
+  SLLM_REQUIRE(rot == 0 || (table != nullptr && max_pos > 0), "qk_norm_rope: rotary table missing");
+  SLLM_REQUIRE(slot_mapping == nullptr || (page_size > 0 && num_pages > 0 && k_cache && v_cache), "qk_norm_rope: cache arguments missing");
+  if (T == 0) return SLLM_OK;
+  const long items = (long)T * (nq + 2 * nkv);
+  const unsigned blocks = (unsigned)((items + 3) / 4);
+#define LAUNCH(TC)                                                                                                        \
+  launch_kernel(qk_norm_rope_kv_write_kernel<TC>, blocks, 128, 0, stream, qkv, ld, q_gain, k_gain, eps, positions, table, rot, \
+                max_pos, nq, nkv, dim, vdim, D, slot_mapping, page_size, num_pages, (TC*)k_cache, (TC*)v_cache, (TC*)q_out, T)
+  if (cache_dtype == SLLM_F32) LAUNCH(float);
+  else if (cache_dtype == SLLM_BF16) LAUNCH(__nv_bfloat16);
+  else SLLM_REQUIRE(false, "qk_norm_rope: unknown dtype %d", cache_dtype);
+#undef LAUNCH
+  return launch_status("qk_norm_rope_kv_write");
+}
+
+SLLM_EXPORT int sllm_short_conv_silu(const float* x, int ld, int off, const float* w, int taps, float* state,
+                                     const int* seq_of_token, const int* q_start, const int* state_slots, float* out, int T,
+                                     int S, int C, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && S >= 0 && C > 0 && taps >= 1 && off >= 0 && off + C <= ld, "short_conv: bad sizes T=%d C=%d taps=%d", T, C, taps);
+  SLLM_REQUIRE(taps == 1 || state != nullptr, "short_conv: a convolution over %d taps needs its state", taps);
+  if (T == 0) return SLLM_OK;
+  const unsigned cb = (unsigned)((C + 255) / 256);
+  launch_kernel(short_conv_silu_kernel, dim3((unsigned)T, cb), 256, 0, stream, x, ld, off, w, taps, (const float*)state,
+                seq_of_token, q_start, state_slots, out, C);
+  int rc = launch_status("short_conv_silu");
+  if (rc != SLLM_OK || taps == 1 || S == 0) return rc;
+  launch_kernel(short_conv_state_kernel, dim3((unsigned)S, cb), 256, 0, stream, x, ld, off, taps, state, q_start, state_slots, C);
+  return launch_status("short_conv_state");
+}
+
+SLLM_EXPORT int sllm_norm_mean_add(float* stream_, const float* a, const float* ga, const float* b, const float* gb, float eps,
+                                   int T, int W, cudaStream_t stream) {
+  SLLM_REQUIRE(T >= 0 && W > 0, "norm_mean_add: bad sizes T=%d W=%d", T, W);
+  if (T == 0) return SLLM_OK;
+  launch_kernel(norm_mean_add_kernel, (unsigned)T, 256, 0, stream, stream_, a, ga, b, gb, eps, W);
+  return launch_status("norm_mean_add");
+}

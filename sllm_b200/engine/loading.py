@@ -35,7 +35,7 @@ def resident_bytes(model: CausalLM) -> int:
         n = 1
         for d in (s.shape if all(d is not None for d in s.shape) else (s.shape_default or ())):
             n *= int(d)
-        total += n * (4 if s.role in ("gain", "bias", "mix") else itemsize)
+        total += n * (4 if s.role in ("gain", "gain_offset", "bias", "mix") else itemsize)
     return total
 
 
@@ -80,8 +80,8 @@ def build_random_model(config: dict, seed: int, dtype="bfloat16", device="cuda:0
     def fetch(name):
         s = specs[name]
         shape = s.concrete_shape()
-        if s.role == "gain":
-            t = torch.ones(shape, dtype=torch.float32, device=device)
+        if s.role in ("gain", "gain_offset"):
+            t = torch.full(shape, 1.0 if s.role == "gain" else 0.0, dtype=torch.float32, device=device)
             if gain_std:
                 t += gain_std * torch.randn(shape, generator=gen, device=device)
             return t

@@ -9,7 +9,8 @@ import torch
 
 from .. import ops
 from ..config.plan import ModelPlan
-from ..parts import delta_rule as _delta_rule, latent_attention as _latent, parallel as _parallel  # noqa: F401
+from ..parts import delta_rule as _delta_rule, experts as _experts, latent_attention as _latent  # noqa: F401
+from ..parts import linear_attention as _linear_attention, parallel as _parallel, side_by_side as _side_by_side  # noqa: F401
 from ..parts import standard as _standard  # noqa: F401  (each import registers its parts)
 from ..parts.base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITIONS, SHIFTS,
                           LayerCache, OwedNorm, StepContext, TensorSpec, join_name)

@@ -203,14 +203,138 @@ def delta_rule(proj, offs, decay, a_bias, state, step, heads: int, dk: int, dv: 
     return out
 
 
-def delta_out(o, gain, proj, off_g: int, eps: float, heads: int, dv: int, out_dtype) -> torch.Tensor:
-    """Each head's ``o`` over its root mean square, times ``gain``, times ``sigmoid`` of the gate logits (columns
-    ``off_g`` of ``proj``), in ``out_dtype``."""
+GATE_ACTS = {"sigmoid": 0, "silu": 1}
+
+
+def delta_out(o, gain, proj, off_g: int, eps: float, heads: int, dv: int, out_dtype, gate_act: str = "sigmoid") -> torch.Tensor:
+    """Each head's ``o`` over its root mean square, times ``gain`` (``[heads*dv]``), times ``sigmoid`` (or ``silu``) of
+    the gate logits (columns ``off_g`` of ``proj``), in ``out_dtype``."""
     _chk(o, gain, proj)
     T = o.shape[0]
     out = torch.empty((T, heads * dv), dtype=out_dtype, device=o.device)
     call("sllm_delta_out", _p(o), _p(gain), _p(proj), proj.shape[1], int(off_g), float(eps), _p(out), _dtc(out_dtype), T, heads, dv,
-         _stream())
+         GATE_ACTS[gate_act], _stream())
+    return out
+
+
+def gated_delta_rule(qkv, offs, gates, off_b: int, off_dt: int, a_log, dt_bias, state, step, heads: int, key_heads: int,
+                     dk: int, dv: int, q_scale: float) -> torch.Tensor:
+    """The gated delta rule over the step's tokens, request by request in token order, from and into the requests' rows
+    of ``state`` (float32 ``[slots, heads, dk, dv]``): S <- g S; w = beta (v - S^T k); S <- S + k w^T; o = S^T q, with k
+    and q made unit vectors per head here (q also times ``q_scale``), beta = sigmoid(b) and g = exp(-exp(A) softplus(a +
+    dt)) one number per head.  ``qkv`` float32 ``[T, ld]`` holds q, k (``key_heads`` heads of ``dk``) and v (``heads`` of
+    ``dv``) at columns ``offs``; ``gates`` float32 ``[T, ldg]`` the logits b and a at columns ``off_b + h``, ``off_dt + h``.
+    Returns ``o`` float32 ``[T, heads*dv]``."""
+    _chk(qkv, gates, a_log, dt_bias, state)
+    T, ld = qkv.shape
+    if qkv.dtype != torch.float32 or gates.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("gated_delta_rule: everything that enters the recurrence is float32")
+    if tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError(f"gated_delta_rule: state {tuple(state.shape)} does not fit {heads} heads of {dk}x{dv}")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=qkv.device)
+    off_q, off_k, off_v = (int(o) for o in offs)
+    call("sllm_gated_delta_rule", _p(qkv), ld, off_q, off_k, off_v, _p(gates), gates.shape[1], int(off_b), int(off_dt), _p(a_log),
+         _p(dt_bias), _p(state), _p(step.q_start), _p(step.state_slots), _p(out), step.num_seqs, heads, key_heads, dk, dv,
+         float(q_scale), int(step.max_q_len), _stream())
+    return out
+
+
+def gated_linear_attention(proj, offs, z, state, step, heads: int, dk: int, dv: int, q_scale: float, tau: float) -> torch.Tensor:
+    """S <- diag(alpha) S + k v^T; o = S^T (q * q_scale) with alpha = sigmoid(z)^(1/tau) per key channel, over the step's
+    tokens from and into ``state`` (float32 ``[slots, heads, dk, dv]``).  ``proj`` float32 ``[T, ld]`` holds q, k, v at
+    columns ``offs``; ``z`` float32 ``[T, heads*dk]``.  Returns ``o`` float32 ``[T, heads*dv]``."""
+    _chk(proj, z, state)
+    T, ld = proj.shape
+    if proj.dtype != torch.float32 or z.dtype != torch.float32 or state.dtype != torch.float32:
+        raise KernelError("gated_linear_attention: everything that enters the recurrence is float32")
+    if tuple(z.shape) != (T, heads * dk) or tuple(state.shape[1:]) != (heads, dk, dv):
+        raise KernelError(f"gated_linear_attention: z {tuple(z.shape)} or state {tuple(state.shape)} does not fit {heads} heads of {dk}x{dv}")
+    out = torch.empty((T, heads * dv), dtype=torch.float32, device=proj.device)
+    off_q, off_k, off_v = (int(o) for o in offs)
+    call("sllm_gated_linear_attention", _p(proj), ld, off_q, off_k, off_v, _p(z), _p(state), _p(step.q_start), _p(step.state_slots),
+         _p(out), step.num_seqs, heads, dk, dv, float(q_scale), 1.0 / float(tau), int(step.max_q_len), _stream())
+    return out
+
+
+# ---- two mixers side by side: normed, rotated attention heads; short convolutions; the normed mean ---------------
+
+def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps: float, positions, table, rotary_dim: int, nq: int, nkv: int, dim: int,
+                          vdim: int, slot_mapping, k_cache, v_cache, out_dtype) -> torch.Tensor:
+    """From a float32 product ``[T, (nq+nkv)*dim + nkv*vdim]``: every query and key head over its root mean square times
+    its gain (``[dim]``, shared by the heads), then rotated; values as they are.  The queries come back ``[T, nq*D]`` in
+    ``out_dtype`` with D the cache's head size (>= dim and vdim; zeros beyond); keys and values go to ``slot_mapping`` in
+    the pages (not written when ``slot_mapping`` is None)."""
+    _chk(qkv, q_gain, k_gain, positions, table, slot_mapping, k_cache, v_cache)
+    T, ld = qkv.shape
+    num_pages, nkv_c, page_size, D = k_cache.shape
+    if qkv.dtype != torch.float32 or nkv_c != nkv or k_cache.dtype != out_dtype or tuple(v_cache.shape) != tuple(k_cache.shape):
+        raise KernelError("qk_norm_rope_kv_write: a float32 product and a cache of the compute dtype [pages, nkv, page_size, D]")
+    max_pos = 0
+    if rotary_dim:
+        if table is None or table.dtype != torch.float32 or tuple(table.shape[1:]) != (2, rotary_dim // 2):
+            raise KernelError("qk_norm_rope_kv_write: rotary table must be float32 [positions, 2, rotary_dim/2]")
+        max_pos = table.shape[0]
+    q = torch.empty((T, nq * D), dtype=out_dtype, device=qkv.device)
+    call("sllm_qk_norm_rope_kv_write", _p(qkv), ld, _p(q_gain), _p(k_gain), float(eps), _p(positions), _p(table), int(rotary_dim),
+         max_pos, nq, nkv, dim, vdim, D, _p(slot_mapping), page_size, num_pages, _p(k_cache), _p(v_cache), _p(q),
+         _dtc(out_dtype), T, _stream())
+    return q
+
+
+def short_conv_silu(x, off: int, weight, state, step) -> torch.Tensor:
+    """``silu`` of a causal convolution over time, per channel, of columns ``off .. off+C`` of the float32 product ``x``:
+    ``weight`` float32 ``[C, taps]`` with the current token's tap last; the ``taps - 1`` inputs before a request's portion
+    come from its row of ``state`` (float32 ``[slots, C, taps-1]``, zeros at a sequence's start), which then receives the
+    portion's last ones.  float32 ``[T, C]``."""
+    _chk(x, weight, state)
+    T, ld = x.shape
+    C, taps = weight.shape
+    if x.dtype != torch.float32 or weight.dtype != torch.float32 or (taps > 1 and tuple(state.shape[1:]) != (C, taps - 1)):
+        raise KernelError("short_conv_silu: float32 input and taps, and a state [slots, C, taps-1]")
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    call("sllm_short_conv_silu", _p(x), ld, int(off), _p(weight), taps, _p(state) if taps > 1 else None, _p(step.seq_of_token),
+         _p(step.q_start), _p(step.state_slots), _p(out), T, step.num_seqs, C, _stream())
+    if taps > 1:
+        launches["own"] += 1          # the state's kernel
+    return out
+
+
+def norm_mean_add_(stream, a, gain_a, b, gain_b, eps: float) -> None:
+    """``stream += (a / rms(a) * gain_a + b / rms(b) * gain_b) / 2`` row by row, all float32."""
+    _chk(stream, a, gain_a, b, gain_b)
+    T, W = stream.shape
+    if any(t.dtype != torch.float32 for t in (stream, a, b, gain_a, gain_b)) or tuple(a.shape) != (T, W) or tuple(b.shape) != (T, W):
+        raise KernelError("norm_mean_add_: float32 [T, W] terms for a float32 stream")
+    call("sllm_norm_mean_add", _p(stream), _p(a), _p(gain_a), _p(b), _p(gain_b), float(eps), T, W, _stream())
+
+
+# ---- a mixture of experts ----------------------------------------------------------------------------------
+
+def moe_route(logits, correction, groups: int, keep: int, top: int, scale: float):
+    """The router's choice from float32 logits ``[T, E]``: (dense weights float32 ``[T, E]`` with zeros for the experts not
+    chosen, indices int32 ``[T, top]``, weights float32 ``[T, top]``).  Scores are sigmoids; the choice goes by score +
+    ``correction`` within the ``keep`` best of ``groups`` groups (a group's score: its two largest choice scores);
+    the weights are the chosen scores times ``scale``."""
+    _chk(logits, correction)
+    T, E = logits.shape
+    if logits.dtype != torch.float32:
+        raise KernelError("moe_route: the router's logits are float32")
+    dense = torch.empty((T, E), dtype=torch.float32, device=logits.device)
+    idx = torch.empty((T, top), dtype=torch.int32, device=logits.device)
+    wts = torch.empty((T, top), dtype=torch.float32, device=logits.device)
+    call("sllm_moe_route", _p(logits), _p(correction), T, E, int(groups), int(keep), int(top), float(scale), _p(dense), _p(idx),
+         _p(wts), _stream())
+    return dense, idx, wts
+
+
+def moe_act(up, dense, ff: int, out_dtype) -> torch.Tensor:
+    """``gelu(up) * weight`` for the routed experts' columns (expert e's at ``e*ff``, weight ``dense[t, e]``) and
+    ``gelu(up)`` for the columns after them; the exact gelu, float32 arithmetic, ``out_dtype`` out."""
+    _chk(up, dense)
+    T, N = up.shape
+    E = dense.shape[1]
+    out = torch.empty((T, N), dtype=out_dtype, device=up.device)
+    call("sllm_moe_act", _p(up), _dt(up), _p(dense), _p(out), _dtc(out_dtype), T, N, E, int(ff), _stream())
     return out
 
 
@@ -929,7 +1053,7 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
     return q
 
 
-def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window):
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None):
     """The CUDA-core attention kernel: any head size up to 256, float32 arithmetic."""
     _chk(q, k_cache, v_cache, block_tables, positions, seq_of_token)
     T = q.shape[0]
@@ -939,7 +1063,7 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     out = torch.empty_like(q)
     call("sllm_attention_simt", _p(q), _p(k_cache), _p(v_cache), _dt(q), _p(block_tables),
          block_tables.shape[1], _p(positions), _p(seq_of_token), T, nq, nkv, hd, page_size, float(scale),
-         int(window or 0), _p(out), _stream())
+         int(window or 0), int(block or 0), _p(out), _stream())
     return out
 
 
@@ -1013,7 +1137,7 @@ def choose_splits(num_small: int, nkv: int, max_ctx: int, ctas_per_sm: int = 2, 
 
 
 def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, decode: bool, num_splits: int,
-                  nq, nkv, hd, scale, window, out=None):
+                  nq, nkv, hd, scale, window, out=None, block=None):
     """The tensor-core attention kernel on one tile list (see `attention_tiles`); the merge of a split context
     touches the rows of that list's requests only."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
@@ -1028,7 +1152,7 @@ def attention_mma(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, de
         part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
     call("sllm_attention_mma", _p(q), _p(k_cache), _p(v_cache), _p(out), _p(part_o), _p(part_lse), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], 1 if decode else 0,
-         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), _stream())
+         num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), int(block or 0), _stream())
     if num_splits > 1:
         launches["own"] += 1          # the combine kernel
     return out
@@ -1045,7 +1169,7 @@ def _tma_ctas_per_sm(hd: int) -> int:
 
 
 def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, num_splits: int,
-                         nq, nkv, hd, scale, window, out=None):
+                         nq, nkv, hd, scale, window, out=None, block=None):
     """The decode form fed by TMA (16-row tiles only; see `attention_tiles`)."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
@@ -1059,7 +1183,7 @@ def attention_tma_decode(q, k_cache, v_cache, block_tables, q_start, ctx_len, ti
         part_lse = torch.empty((num_splits, T, nq), dtype=torch.float32, device=q.device)
     call("sllm_attention_tma_decode", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(part_o),
          _p(part_lse), _p(block_tables), block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]),
-         tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0),
+         tiles[2], num_splits, T, nq, nkv, hd, k_cache.shape[2], float(scale), int(window or 0), int(block or 0),
          _p(_status_word(q.device)), _stream())
     _tc_used["since_check"] += 1
     if num_splits > 1:
@@ -1128,8 +1252,10 @@ def mma_supports(hd: int) -> bool:
     return bool(lib().sllm_attention_mma_supports(int(hd)))
 
 
-def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window):
-    """Causal attention of the step's tokens over their requests' pages.  bfloat16 with a head size
+def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, window, block=None):
+    """Causal attention of the step's tokens over their requests' pages.  ``window``: only the last ``window`` keys;
+    ``block``: only the keys of the query's own block of ``block`` positions, counted from the sequence's start (both
+    run on the mma.sync and TMA-fed forms, not on tcgen05).  bfloat16 with a head size
     the tensor-core kernels take: requests of at most 16 (token, head-in-group) rows go to the decode
     form (fed by TMA where the head and page sizes allow, split over the context), the others to the
     prefill form in 128-row tiles (on tcgen05 where there is no window and the sizes allow, else on
@@ -1137,10 +1263,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     g = step.groups[group]
     if q.dtype != torch.bfloat16 or not mma_supports(hd):
         return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
-                              nq, nkv, hd, scale, window)
+                              nq, nkv, hd, scale, window, block)
     G = nq // nkv
-    use_tc = not window and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
-    key = ("mma", G, nkv, use_tc)
+    use_tc = not window and not block and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
+    key = ("mma", G, nkv, use_tc, block or 0)
     if key not in step.attn_tiles:
         # 128-row CTAs, two per SM.  (The kernel also has a form with two row tiles a CTA, one CTA per SM,
         # that fetches each key/value tile once for 256 rows; measured at 28/4 heads of 128 it is the
@@ -1162,16 +1288,16 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
-                             nq, nkv, hd, scale, window, out)
+                             nq, nkv, hd, scale, window, out, block)
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
-                      nq, nkv, hd, scale, window, out)
+                      nq, nkv, hd, scale, window, out, block)
     if large and use_tc:
         attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
                      row_tiles=rows // 128, splits=tc_splits)
     elif large:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, False, 1,
-                      nq, nkv, hd, scale, window, out)
+                      nq, nkv, hd, scale, window, out, block)
     return out
 
 

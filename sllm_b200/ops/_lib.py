@@ -50,7 +50,19 @@ def _declare(L):
         "sllm_delta_rule_supports": [c_int, c_int],
         "sllm_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
                             c_int, c_int, c_int, c_int, c_int, c_void_p],
-        "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_delta_out": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_float, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
+        "sllm_gated_delta_rule": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                                  c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_void_p],
+        "sllm_gated_linear_attention": [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                                        c_int, c_int, c_int, c_int, c_float, c_float, c_int, c_void_p],
+        "sllm_qk_norm_rope_kv_write": [c_void_p, c_int, c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_int, c_int,
+                                       c_int, c_int, c_int, c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                                       c_void_p],
+        "sllm_short_conv_silu": [c_void_p, c_int, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                 c_int, c_int, c_void_p],
+        "sllm_norm_mean_add": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_int, c_void_p],
+        "sllm_moe_route": [c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_void_p],
+        "sllm_moe_act": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p],
         "sllm_latent_write": [c_void_p, c_int, c_int, c_int, c_void_p, c_float, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "sllm_head_linear": [c_void_p, c_int, c_int, c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int,
                              c_int, c_int, c_void_p],
@@ -62,7 +74,7 @@ def _declare(L):
                                c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p],
         "sllm_gemm_f32": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
         "sllm_attention_simt": [c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int,
-                                c_int, c_int, c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                c_int, c_int, c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
         "sllm_sample_rows": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p],
         "sllm_repetition_penalty": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
         "sllm_mark_seen": [c_void_p, c_int, c_int, c_void_p, c_void_p, c_void_p, c_int, c_void_p],
@@ -72,7 +84,7 @@ def _declare(L):
         "sllm_attention_tma_ctas_per_sm": [c_int],
         "sllm_attention_tma_decode": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_void_p, c_void_p,
                                       c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
-                                      c_int, c_int, c_float, c_int, c_void_p, c_void_p],
+                                      c_int, c_int, c_float, c_int, c_int, c_void_p, c_void_p],
         "sllm_wait_probe": [c_void_p, ctypes.c_ulonglong, c_void_p, c_void_p],
         "sllm_attention_tc_supports": [c_int, c_int],
         "sllm_attention_tc": [c_void_p, c_void_p, c_void_p, ctypes.c_longlong, c_void_p, c_void_p, c_int, c_void_p, c_void_p,
@@ -105,7 +117,7 @@ def _declare(L):
                                c_int, c_void_p],
         "sllm_attention_mma": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
                                c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
-                               c_int, c_int, c_float, c_int, c_void_p],
+                               c_int, c_int, c_float, c_int, c_int, c_void_p],
     }
     for name, argtypes in sigs.items():
         fn = getattr(L, name)

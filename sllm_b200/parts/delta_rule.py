@@ -1,4 +1,7 @@
-"""A recurrent mixer: the generalized delta rule.
+"""Recurrent mixers of the delta-rule family: the generalized delta rule, and the gated delta rule behind short
+convolutions (`GatedDelta`, at the end of the file).
+
+The generalized delta rule:
 
 Per head a float32 matrix state S [key channel, value channel] that every token decays per key channel, frees along
 its unit key at a per-channel rate, and writes its key-value product into:
@@ -78,3 +81,76 @@ class GeneralDelta(Mixer):
 
     def weight_bytes(self):
         return self.inp.nbytes() + self.w2.nbytes() + self.out.nbytes() + 8 * self.C
+
+
+@MIXERS.register("gated_delta")
+class GatedDelta(Mixer):
+    """The gated delta rule.  Per head a float32 matrix state S [key channel, value channel]:
+
+        S <- g S;    w = beta (v - S^T k);    S <- S + k w^T;    o = S^T q      (the read-out sees the token's own write)
+
+    q = W_q x and k = W_k x (``kv_heads`` heads of ``dim``), v = W_v x (``heads`` heads of ``vdim``; head h reads q/k head
+    h // (heads / kv_heads)); each passes a causal convolution over ``conv`` taps per channel and silu; q and k become unit
+    vectors per head (x / sqrt(sum(x^2) + 1e-6)), q also times dim^(-1/2); beta = sigmoid(W_b x) and the decay g =
+    exp(-exp(A_log) softplus(W_a x + dt_bias)), one number per head.  Each head's o over its root mean square (``eps``) times
+    a gain shared by the heads, times silu(W_g x), then W_o.  Two states per request: the matrix, and the convolution's
+    last ``conv`` - 1 inputs.  All six projections are one matrix whose product stays float32."""
+
+    NAMES = ("q", "k", "v", "b", "a", "g")
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.kv_heads = int(params.get("kv_heads", self.heads))
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.taps = int(params.get("conv", 1))
+        self.eps = float(params["eps"])
+        if self.heads % self.kv_heads:
+            raise ValueError(f"gated_delta: {self.heads} heads are no multiple of {self.kv_heads} query/key heads")
+        if self.taps < 1:
+            raise ValueError(f"gated_delta: conv={self.taps} must be at least 1")
+        if not ops.delta_rule_supports(self.dim, self.vdim):
+            raise ValueError(f"gated_delta: a head of {self.dim} key channels is outside what the recurrence kernel keeps in registers (1..256)")
+        self.K, self.V = self.kv_heads * self.dim, self.heads * self.vdim
+        self.C = 2 * self.K + self.V            # channels that pass the convolution
+
+    def cache_need(self):
+        needs = [SlotState((self.heads, self.dim, self.vdim), "delta")]
+        if self.taps > 1:
+            needs.append(SlotState((self.C, self.taps - 1), "conv"))
+        return tuple(needs)
+
+    def tensor_specs(self):
+        H, W, K, V, t = self.heads, self.hidden, self.K, self.V, self.taps
+        return [TensorSpec("q", (K, W)), TensorSpec("q.conv", (K, t), role="bias"), TensorSpec("k", (K, W)),
+                TensorSpec("k.conv", (K, t), role="bias"), TensorSpec("v", (V, W)), TensorSpec("v.conv", (V, t), role="bias"),
+                TensorSpec("b", (H, W)), TensorSpec("A_log", (H,), role="bias"), TensorSpec("norm", (self.vdim,), role="gain"),
+                TensorSpec("a", (H, W)), TensorSpec("dt_bias", (H,), role="bias"), TensorSpec("g", (V, W)), TensorSpec("o", (W, V))]
+
+    def bind(self, fetch):
+        H = self.heads
+        self.inp = Linear(self._matrix(torch.cat([fetch(n) for n in self.NAMES], dim=0)))
+        self.offs = (0, self.K, 2 * self.K)
+        self.off_b, self.off_a, self.off_g = self.C, self.C + H, self.C + 2 * H
+        self.conv_w = self._f32(torch.cat([fetch(f"{n}.conv").float() for n in ("q", "k", "v")], dim=0))
+        self.a_log = self._f32(fetch("A_log"))
+        self.dt_bias = self._f32(fetch("dt_bias"))
+        self.gain = self._f32(fetch("norm").float().repeat(H))
+        self.out = Linear(self._matrix(fetch("o")))
+
+    accepts_residual = True
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True):
+        proj = self.inp(x, torch.float32)                                            # [T, C + 2H + V] float32
+        cv = ops.short_conv_silu(proj, 0, self.conv_w, cache.states.get("conv"), step)      # [T, C] float32
+        o = ops.gated_delta_rule(cv, self.offs, proj, self.off_b, self.off_a, self.a_log, self.dt_bias, cache.states["delta"],
+                                 step, self.heads, self.kv_heads, self.dim, self.vdim, self.dim ** -0.5)
+        return ops.delta_out(o, self.gain, proj, self.off_g, self.eps, self.heads, self.vdim, self.dtype, "silu")
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        return self.out.into(self.mix(x, step, cache, position, write_cache), residual)
+
+    def weight_bytes(self):
+        return self.inp.nbytes() + self.out.nbytes() + 4 * (self.conv_w.numel() + self.gain.numel() + 2 * self.heads)

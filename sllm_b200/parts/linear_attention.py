@@ -1,0 +1,82 @@
+"""Gated linear attention: a recurrent mixer whose float32 matrix state per head decays per key channel.
+
+    S_t = diag(alpha_t) S_(t-1) + k_t v_t^T,        o_t = S_t^T q_t
+
+with q = W_q x * dim^(-1/2), k = W_k x (heads x dim), v = W_v x (heads x vdim) and a decay per key channel from a
+low-rank pair of products: alpha = sigmoid(W_a2 (W_a1 x) + b)^(1/tau).  Each head's o over its root mean square times a
+gain shared by the heads, times silu(W_g x), then W_o.  The state starts at zero and lives in the request's state slot,
+so a prompt's portions and single decoded tokens continue one another.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from .base import MIXERS, LayerCache, Mixer, SlotState, StepContext, TensorSpec
+from .standard import Linear
+
+
+@MIXERS.register("gated_linear_attention")
+class GatedLinearAttention(Mixer):
+    """Parameters: ``hidden_size``, ``heads``, ``dim``, ``vdim``, ``tau``, ``eps`` (of the output's norm); the decay's
+    rank is read from the checkpoint (``decay_rank`` for random weights).  q, k, v and the gate are one matrix, its
+    product stays float32, as everything that enters the recurrence does."""
+
+    NAMES = ("q", "k", "v", "g")
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.heads = int(params["heads"])
+        self.dim = int(params["dim"])
+        self.vdim = int(params["vdim"])
+        self.tau = float(params["tau"])
+        self.eps = float(params["eps"])
+        self.rank = params.get("decay_rank")
+        if not ops.delta_rule_supports(self.dim, self.vdim):
+            raise ValueError(f"gated_linear_attention: a head of {self.dim} key channels is outside what the recurrence kernel "
+                             f"keeps in registers (1..256)")
+        if not self.tau > 0:
+            raise ValueError(f"gated_linear_attention: tau={self.tau} must be positive")
+
+    def cache_need(self):
+        return SlotState((self.heads, self.dim, self.vdim), "gla")
+
+    def tensor_specs(self):
+        H, W, R = self.heads, self.hidden, self.rank
+        K, V = H * self.dim, H * self.vdim
+        default = max(4, min(64, W // 16))
+        return [TensorSpec("q", (K, W)), TensorSpec("k", (K, W)), TensorSpec("v", (V, W)), TensorSpec("g", (V, W)),
+                TensorSpec("o", (W, V)), TensorSpec("norm", (self.vdim,), role="gain"),
+                TensorSpec("a1", (R, W), shape_default=(R or default, W)), TensorSpec("a2", (K, R), shape_default=(K, R or default)),
+                TensorSpec("a2.b", (K,), role="bias")]
+
+    def bind(self, fetch):
+        H = self.heads
+        K, V = H * self.dim, H * self.vdim
+        self.rank = int(fetch("a1").shape[0])
+        if tuple(fetch("a2").shape) != (K, self.rank):
+            raise ValueError(f"gated_linear_attention: a2 {tuple(fetch('a2').shape)} does not fit a1's {self.rank} rows")
+        self.inp = Linear(self._matrix(torch.cat([fetch(n) for n in self.NAMES], dim=0)))
+        self.offs = (0, K, 2 * K)
+        self.off_g = 2 * K + V
+        self.a1 = Linear(self._matrix(fetch("a1")))
+        self.a2 = Linear(self._matrix(fetch("a2")), self._f32(fetch("a2.b")))
+        self.gain = self._f32(fetch("norm").float().repeat(H))
+        self.out = Linear(self._matrix(fetch("o")))
+
+    accepts_residual = True
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True):
+        proj = self.inp(x, torch.float32)                                            # [T, 2K + 2V] float32
+        z = self.a2(self.a1(x, self.dtype), torch.float32)                           # [T, K] decay logits, float32
+        o = ops.gated_linear_attention(proj, self.offs, z, cache.states["gla"], step, self.heads, self.dim, self.vdim,
+                                       self.dim ** -0.5, self.tau)                   # [T, V] float32
+        return ops.delta_out(o, self.gain, proj, self.off_g, self.eps, self.heads, self.vdim, self.dtype, "silu")
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        return self.out.into(self.mix(x, step, cache, position, write_cache), residual)
+
+    def weight_bytes(self):
+        return self.inp.nbytes() + self.a1.nbytes() + self.a2.nbytes() + self.out.nbytes() + 4 * self.gain.numel()

@@ -21,22 +21,31 @@ from .standard import Linear
 class GroupRMSNorm(Norm):
     """The vector in ``groups`` equal consecutive parts, each divided by its own sqrt(mean(part^2) + eps); the
     whole times a plain gain.  float32 on the float32 stream.  ``groups`` = 1 is the ordinary RMS norm.  The gain
-    is the tensor that carries the norm's own name."""
+    is the tensor that carries the norm's own name.  ``offset``: the stored tensor is the gain minus this (a gain kept
+    around zero has ``offset`` 1); ``gain_scale``: a constant the output is multiplied by as well (a model whose output
+    head scales its logits puts the factor here, into its last norm)."""
 
     def __init__(self, params, **kw):
         super().__init__(params, **kw)
         self.size = int(params["size"])
         self.groups = int(params.get("groups", 1))
         self.eps = float(params["eps"])
+        self.offset = float(params.get("offset", 0.0))
+        self.gain_scale = float(params.get("gain_scale", 1.0))
         if self.groups < 1 or self.size % self.groups:
             raise ValueError(f"group_rmsnorm: {self.groups} groups do not divide {self.size}")
         self.weight = None
 
     def tensor_specs(self):
-        return [TensorSpec("", (self.size,), role="gain")]
+        return [TensorSpec("", (self.size,), role="gain" if self.offset == 0.0 else "gain_offset")]
 
     def bind(self, fetch):
-        self.weight = self._f32(fetch(""))
+        w = self._f32(fetch(""))
+        if self.offset != 0.0:
+            w = w + self.offset
+        if self.gain_scale != 1.0:
+            w = w * self.gain_scale
+        self.weight = w.contiguous()
 
     def complete(self, residual, delta) -> None:
         """Add what a block before has left pending into the stream (nothing to do when its products added their

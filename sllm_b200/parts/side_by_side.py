@@ -1,0 +1,158 @@
+"""Two mixers side by side on one input, and the attention one of them usually is.
+
+`NormedAttention`: grouped-query softmax attention over the paged cache whose query and key heads are RMS-normed (one
+gain of the head's size, shared by the heads) before they are rotated; it owns its rotary table (each layer may have
+other frequencies, and a two-regime frequency scaling); a query may be restricted to the keys of its own block of
+positions; the value size may differ from the key size.
+
+`SideBySide`: both mixers read the same input; the layer's term is the mean of their outputs, each first RMS-normed over
+the model width with a gain of its own.
+"""
+
+from __future__ import annotations
+
+import torch
+
+from .. import ops
+from ..config.plan import PartSpec
+from .base import MIXERS, POSITIONS, LayerCache, Mixer, PagedKV, StepContext, TensorSpec, flatten_needs
+from .standard import Linear
+
+_TABLES: dict = {}       # rotary tables by their parameters: layers with the same frequencies share one
+
+
+def rotary_for(params: dict, dtype, device):
+    sc = params.get("scaling")
+    key = (float(params["theta"]), int(params["rotary_dim"]), int(params["max_positions"]),
+           tuple(sorted((k, float(v)) for k, v in sc.items())) if sc else None, str(device))
+    if key not in _TABLES:
+        _TABLES[key] = POSITIONS.build(PartSpec("rotary", dict(params)), dtype=dtype, device=device)
+    return _TABLES[key]
+
+
+@MIXERS.register("normed_attention")
+class NormedAttention(Mixer):
+    """Parameters: ``hidden_size``, ``heads``, ``kv_heads``, ``dim`` (query/key size of a head), ``vdim`` (value size),
+    ``scale`` (of the scores), ``eps`` (of the head norms), ``rotary`` (None, or ``theta``, ``rotary_dim``, optional
+    ``scaling``: see `parts.standard.Rotary`), ``block`` (None, or the size of the blocks of positions, counted from 0,
+    inside which a query sees the keys at or before it), ``max_positions``.
+
+    The cache's head holds max(dim, vdim) channels (rounded up to a size the tensor-core kernels take, in bfloat16):
+    keys and values are stored with zeros beyond their own size, which neither scores nor sums see; the output
+    projection's matrix has zero columns there."""
+
+    MAX_HEAD = 256
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        p = params
+        self.hidden = int(p["hidden_size"])
+        self.nq, self.nkv = int(p["heads"]), int(p["kv_heads"])
+        self.dim, self.vdim = int(p["dim"]), int(p["vdim"])
+        self.scale = float(p["scale"])
+        self.eps = float(p["eps"])
+        self.block = int(p["block"]) if p.get("block") else None
+        self.max_positions = int(p["max_positions"])
+        rot = p.get("rotary")
+        self.rot_params = dict(rot, max_positions=self.max_positions) if rot else None
+        self.rot = int(rot["rotary_dim"]) if rot else 0
+        if self.nq % self.nkv:
+            raise ValueError(f"normed_attention: {self.nq} query heads are no multiple of {self.nkv} key/value heads")
+        if self.rot % 2 or self.rot > self.dim:
+            raise ValueError(f"normed_attention: {self.rot} rotated channels must be even and at most dim={self.dim}")
+        D = max(self.dim, self.vdim)
+        if not 1 <= D <= self.MAX_HEAD:
+            raise ValueError(f"normed_attention: a head of {D} channels is outside 1..{self.MAX_HEAD}, the largest the attention kernels take")
+        if self.dtype == torch.bfloat16:
+            D = next((s for s in (16, 32, 64, 128) if s >= D), D)
+        self.D = D
+        self.rotary = None
+
+    def cache_need(self):
+        return PagedKV(self.nkv, self.D, None)
+
+    def tensor_specs(self):
+        W = self.hidden
+        return [TensorSpec("q", (self.nq * self.dim, W)), TensorSpec("k", (self.nkv * self.dim, W)),
+                TensorSpec("v", (self.nkv * self.vdim, W)), TensorSpec("q.norm", (self.dim,), role="gain"),
+                TensorSpec("k.norm", (self.dim,), role="gain"), TensorSpec("o", (W, self.nq * self.vdim))]
+
+    def bind(self, fetch):
+        self.qkv = Linear(self._matrix(torch.cat([fetch(n) for n in ("q", "k", "v")], dim=0)))
+        self.q_gain, self.k_gain = self._f32(fetch("q.norm")), self._f32(fetch("k.norm"))
+        o = fetch("o")
+        if self.D != self.vdim:
+            wide = torch.zeros((self.hidden, self.nq, self.D), dtype=o.dtype)
+            wide[:, :, :self.vdim] = o.reshape(self.hidden, self.nq, self.vdim)
+            o = wide.reshape(self.hidden, self.nq * self.D)
+        self.out = Linear(self._matrix(o))
+        if self.rot_params is not None:
+            self.rotary = rotary_for(self.rot_params, self.dtype, self.device)
+
+    accepts_residual = True
+
+    def mix(self, x, step: StepContext, cache: LayerCache, position=None, write_cache=True):
+        g = step.groups[cache.group]
+        qkv = self.qkv(x, torch.float32)                                             # [T, (nq+nkv) dim + nkv vdim] float32
+        q = ops.qk_norm_rope_kv_write(qkv, self.q_gain, self.k_gain, self.eps, step.positions,
+                                      self.rotary.table if self.rotary is not None else None, self.rot, self.nq, self.nkv,
+                                      self.dim, self.vdim, g.slot_mapping if write_cache else None, cache.k, cache.v, self.dtype)
+        return ops.paged_attention(q, cache.k, cache.v, step, cache.group, self.nq, self.nkv, self.D, self.scale, None, self.block)
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        return self.out.into(self.mix(x, step, cache, position, write_cache), residual)
+
+    def weight_bytes(self):
+        return self.qkv.nbytes() + self.out.nbytes() + 8 * self.dim
+
+
+@MIXERS.register("side_by_side")
+class SideBySide(Mixer):
+    """Parameters: ``hidden_size``, ``eps``, and ``left`` and ``right``, each ``{"kind": ..., "params": {...}}`` naming a
+    registered mixer that offers ``mix(x, step, cache, position, write_cache)`` (its output before the projection) and
+    ``out`` (that projection).  Tensors: the mixers' under ``left.`` and ``right.``, and the gains ``left.out`` and
+    ``right.out`` of the model's width.  What the two ask of the cache manager is asked together (at most one of them
+    pages; state names must differ)."""
+
+    SIDES = ("left", "right")
+
+    def __init__(self, params, **kw):
+        super().__init__(params, **kw)
+        self.hidden = int(params["hidden_size"])
+        self.eps = float(params["eps"])
+        self.sides = [MIXERS.build(PartSpec(params[s]["kind"], params[s]["params"]), **kw) for s in self.SIDES]
+        for s, m in zip(self.SIDES, self.sides):
+            if not hasattr(m, "mix"):
+                raise ValueError(f"side_by_side: the {s} mixer ({params[s]['kind']}) does not offer its output before the projection")
+
+    def cache_need(self):
+        needs = []
+        for m in self.sides:
+            needs.extend(flatten_needs(m.cache_need()))
+        return tuple(needs) if needs else None
+
+    def tensor_specs(self):
+        specs = []
+        for s, m in zip(self.SIDES, self.sides):
+            specs.extend(t.prefixed(s) for t in m.tensor_specs())
+        specs += [TensorSpec(f"{s}.out", (self.hidden,), role="gain") for s in self.SIDES]
+        return specs
+
+    def bind(self, fetch):
+        for s, m in zip(self.SIDES, self.sides):
+            m.bind(lambda rel, _s=s: fetch(f"{_s}.{rel}"))
+        self.gains = [self._f32(fetch(f"{s}.out")) for s in self.SIDES]
+
+    accepts_residual = True
+
+    def forward(self, x, step, cache, position, write_cache=True, residual=None):
+        a, b = (m.out(m.mix(x, step, cache, position, write_cache), torch.float32) for m in self.sides)    # [T, W] float32 each
+        if residual is None:
+            residual = torch.zeros_like(a)
+            ops.norm_mean_add_(residual, a, self.gains[0], b, self.gains[1], self.eps)
+            return residual
+        ops.norm_mean_add_(residual, a, self.gains[0], b, self.gains[1], self.eps)
+        return None
+
+    def weight_bytes(self):
+        return sum(m.weight_bytes() for m in self.sides) + 8 * self.hidden

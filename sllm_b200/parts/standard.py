@@ -86,7 +86,13 @@ class Rotary(PositionEncoding):
     """Rotate-half rotary encoding over the first ``rotary_dim`` dims of a head:
     angle(pos, j) = pos * theta^(-2j/rot), j < rot/2 (ref/qwen3_5.py:343-352).
     The table of cos and sin is computed once in float64 and stored in float32,
-    ``[max_positions, rot/2]`` each."""
+    ``[max_positions, rot/2]`` each.
+
+    ``scaling`` (optional; ``factor``, ``original``, ``fast``, ``slow``) stretches the slow channels for contexts beyond
+    ``original`` positions and leaves the fast ones alone: with c(t) = rot * ln(original / (2 pi t)) / (2 ln theta) the
+    channel that turns t times over the original context, lo = max(floor(c(fast)), 0), hi = min(ceil(c(slow)), rot - 1)
+    and ramp_j = clamp((j - lo) / max(hi - lo, 0.001), 0, 1), channel j's frequency becomes f_j / factor * ramp_j +
+    f_j * (1 - ramp_j), and cos and sin are multiplied by 0.1 ln(factor) + 1."""
 
     def __init__(self, params, **kw):
         super().__init__(params, **kw)
@@ -94,11 +100,27 @@ class Rotary(PositionEncoding):
         self.rotary_dim = int(params["rotary_dim"])
         self.max_positions = int(params["max_positions"])
         half = self.rotary_dim // 2
-        inv_freq = 1.0 / (self.theta ** (np.arange(0, self.rotary_dim, 2, dtype=np.float64) / self.rotary_dim))
+        inv_freq, magnitude = self.frequencies(self.theta, self.rotary_dim, params.get("scaling"))
         ang = np.arange(self.max_positions, dtype=np.float64)[:, None] * inv_freq[None, :]
-        table = np.stack([np.cos(ang), np.sin(ang)], axis=1).astype(np.float32)   # [P, 2, half]
+        table = (np.stack([np.cos(ang), np.sin(ang)], axis=1) * magnitude).astype(np.float32)   # [P, 2, half]
         assert table.shape == (self.max_positions, 2, half)
         self.table = torch.from_numpy(table).to(self.device).contiguous()
+
+    @staticmethod
+    def frequencies(theta: float, rot: int, scaling=None):
+        """(float64 frequencies ``[rot/2]``, the factor on cos and sin)."""
+        j = np.arange(rot // 2, dtype=np.float64)
+        f = theta ** (-2.0 * j / rot)
+        if not scaling:
+            return f, 1.0
+        factor, original = float(scaling["factor"]), float(scaling["original"])
+
+        def channel(turns):
+            return rot * np.log(original / (2.0 * np.pi * turns)) / (2.0 * np.log(theta))
+        lo = max(int(np.floor(channel(float(scaling["fast"])))), 0)
+        hi = min(int(np.ceil(channel(float(scaling["slow"])))), rot - 1)
+        ramp = np.clip((j - lo) / max(hi - lo, 0.001), 0.0, 1.0)
+        return f / factor * ramp + f * (1.0 - ramp), 0.1 * float(np.log(factor)) + 1.0
 
 
 @MIXERS.register("attention")
@@ -252,15 +274,17 @@ class SwiGLU(FeedForward):
 class PreNormBlock:
     """h += mixer(norm1(h)); h += ffn(norm2(h)) (ref/standard.py:102-129).  The
     addition of each term is done by the norm that follows it, so the block
-    takes the pending term of the layer before and hands its own on."""
+    takes the pending term of the layer before and hands its own on.  A layer
+    may come without a feed-forward (no ``ffn``, no ``ffn_norm``): then the
+    mixer's term is the one handed on."""
 
     ROLES = ("mixer", "ffn", "mixer_norm", "ffn_norm")
 
     def __init__(self, parts: dict):
-        if set(parts) != set(self.ROLES):
-            raise ValueError(f"the pre-norm block arranges {self.ROLES}; the layer names {sorted(parts)}")
-        self.mixer, self.ffn = parts["mixer"], parts["ffn"]
-        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts["ffn_norm"]
+        if set(parts) != set(self.ROLES) and set(parts) != {"mixer", "mixer_norm"}:
+            raise ValueError(f"the pre-norm block arranges {self.ROLES} (or mixer and mixer_norm alone); the layer names {sorted(parts)}")
+        self.mixer, self.ffn = parts["mixer"], parts.get("ffn")
+        self.mixer_norm, self.ffn_norm = parts["mixer_norm"], parts.get("ffn_norm")
 
     def cache_need(self):
         return self.mixer.cache_need()
@@ -292,6 +316,8 @@ class PreNormBlock:
         x = self._normed(self.mixer_norm, residual, delta)
         if isinstance(x, OwedNorm) and not getattr(self.mixer, "accepts_next_norm", False):
             x = x.plain()
+        if self.ffn is None:
+            return self._call(self.mixer, x, step, cache, position, write_cache, residual=residual, next_norm=next_norm)
         d = self._call(self.mixer, x, step, cache, position, write_cache, residual=residual, next_norm=self.ffn_norm)
         x = self._normed(self.ffn_norm, residual, d)
         if isinstance(x, OwedNorm) and not getattr(self.ffn, "accepts_next_norm", False):

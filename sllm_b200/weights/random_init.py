@@ -35,6 +35,8 @@ def random_tensors(specs, seed: int, *, std: float = 0.02, bias_std: float | Non
         shape = s.concrete_shape()
         if s.role == "gain":
             a = 1.0 + gain_std * rng.standard_normal(shape, dtype=np.float32) if gain_std else np.ones(shape, np.float32)
+        elif s.role == "gain_offset":      # a gain stored as its distance from one
+            a = gain_std * rng.standard_normal(shape, dtype=np.float32) if gain_std else np.zeros(shape, np.float32)
         elif s.role == "bias":
             a = bias_std * rng.standard_normal(shape, dtype=np.float32)
         elif s.role == "mix":              # a blend between two vectors, per channel: values in (0, 1)

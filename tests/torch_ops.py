@@ -96,11 +96,140 @@ def delta_rule(proj, offs, decay, a_bias, state, step, heads, dk, dv):
     return out.reshape(T, heads * dv)
 
 
-def delta_out(o, gain, proj, off_g, eps, heads, dv, out_dtype):
+def delta_out(o, gain, proj, off_g, eps, heads, dv, out_dtype, gate_act="sigmoid"):
     T = o.shape[0]
     x = o.reshape(T, heads, dv)
     x = x * (x.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
-    return (x.reshape(T, heads * dv) * gain * torch.sigmoid(proj[:, off_g:off_g + heads * dv])).to(out_dtype)
+    g = proj[:, off_g:off_g + heads * dv]
+    gate = torch.sigmoid(g) if gate_act == "sigmoid" else g * torch.sigmoid(g)
+    return (x.reshape(T, heads * dv) * gain * gate).to(out_dtype)
+
+
+def _walk(step, state, out, token):
+    """Request by request, token by token: ``token(t, S) -> (S, o)`` from and into the requests' state rows."""
+    starts = step.q_start.long().tolist()
+    for s in range(step.num_seqs):
+        slot = int(step.state_slots[s])
+        S = state[slot].clone()
+        for t in range(starts[s], starts[s + 1]):
+            S, out[t] = token(t, S)
+        state[slot] = S
+
+
+def gated_delta_rule(qkv, offs, gates, off_b, off_dt, a_log, dt_bias, state, step, heads, key_heads, dk, dv, q_scale):
+    T = qkv.shape[0]
+    off_q, off_k, off_v = offs
+    rep = heads // key_heads
+    q = qkv[:, off_q:off_q + key_heads * dk].reshape(T, key_heads, dk)
+    k = qkv[:, off_k:off_k + key_heads * dk].reshape(T, key_heads, dk)
+    v = qkv[:, off_v:off_v + heads * dv].reshape(T, heads, dv)
+    q = (q / torch.sqrt((q * q).sum(-1, keepdim=True) + 1e-6) * q_scale).repeat_interleave(rep, dim=1)
+    k = (k / torch.sqrt((k * k).sum(-1, keepdim=True) + 1e-6)).repeat_interleave(rep, dim=1)
+    beta = torch.sigmoid(gates[:, off_b:off_b + heads])
+    g = torch.exp(-torch.exp(a_log) * torch.nn.functional.softplus(gates[:, off_dt:off_dt + heads] + dt_bias))
+    out = torch.empty((T, heads, dv), dtype=torch.float32, device=qkv.device)
+
+    def token(t, S):
+        S = g[t][:, None, None] * S
+        w = beta[t][:, None] * (v[t] - torch.einsum("hij,hi->hj", S, k[t]))
+        S = S + k[t][:, :, None] * w[:, None, :]
+        return S, torch.einsum("hij,hi->hj", S, q[t])
+    _walk(step, state, out, token)
+    return out.reshape(T, heads * dv)
+
+
+def gated_linear_attention(proj, offs, z, state, step, heads, dk, dv, q_scale, tau):
+    T = proj.shape[0]
+    off_q, off_k, off_v = offs
+    q = proj[:, off_q:off_q + heads * dk].reshape(T, heads, dk) * q_scale
+    k = proj[:, off_k:off_k + heads * dk].reshape(T, heads, dk)
+    v = proj[:, off_v:off_v + heads * dv].reshape(T, heads, dv)
+    alpha = torch.exp(torch.nn.functional.logsigmoid(z) / tau).reshape(T, heads, dk)
+    out = torch.empty((T, heads, dv), dtype=torch.float32, device=proj.device)
+
+    def token(t, S):
+        S = alpha[t][:, :, None] * S + k[t][:, :, None] * v[t][:, None, :]
+        return S, torch.einsum("hij,hi->hj", S, q[t])
+    _walk(step, state, out, token)
+    return out.reshape(T, heads * dv)
+
+
+def qk_norm_rope_kv_write(qkv, q_gain, k_gain, eps, positions, table, rotary_dim, nq, nkv, dim, vdim, slot_mapping, k_cache, v_cache,
+                          out_dtype):
+    T = qkv.shape[0]
+    D = k_cache.shape[3]
+    qk = qkv[:, :(nq + nkv) * dim].float().reshape(T, nq + nkv, dim)
+    v = qkv[:, (nq + nkv) * dim:(nq + nkv) * dim + nkv * vdim].float().reshape(T, nkv, vdim)
+    qk = qk * (qk.pow(2).mean(-1, keepdim=True) + eps).rsqrt()
+    qk = torch.cat([qk[:, :nq] * q_gain, qk[:, nq:] * k_gain], dim=1)
+    if rotary_dim:
+        half = rotary_dim // 2
+        cs = table[positions.long()]
+        c, s = cs[:, None, 0, :], cs[:, None, 1, :]
+        x1, x2 = qk[..., :half], qk[..., half:rotary_dim]
+        qk = torch.cat([x1 * c - x2 * s, x2 * c + x1 * s, qk[..., rotary_dim:]], dim=-1)
+    qk = torch.nn.functional.pad(qk, (0, D - dim))
+    v = torch.nn.functional.pad(v, (0, D - vdim))
+    if slot_mapping is not None:
+        ps = k_cache.shape[2]
+        ok = slot_mapping >= 0
+        page, off = slot_mapping[ok].long() // ps, slot_mapping[ok].long() % ps
+        k_cache[page, :, off, :] = qk[ok][:, nq:].to(k_cache.dtype)
+        v_cache[page, :, off, :] = v[ok].to(v_cache.dtype)
+    return qk[:, :nq].reshape(T, nq * D).to(out_dtype)
+
+
+def short_conv_silu(x, off, weight, state, step):
+    C, taps = weight.shape
+    T = x.shape[0]
+    out = torch.empty((T, C), dtype=torch.float32, device=x.device)
+    starts = step.q_start.long().tolist()
+    for s in range(step.num_seqs):
+        a, b = starts[s], starts[s + 1]
+        slot = int(step.state_slots[s])
+        xs = x[a:b, off:off + C].float()
+        before = state[slot].t() if taps > 1 else xs[:0]                 # [taps-1, C], oldest first
+        padded = torch.cat([before, xs], dim=0)
+        acc = torch.zeros((b - a, C), dtype=torch.float32, device=x.device)
+        for j in range(taps):
+            acc += padded[j:j + b - a] * weight[:, j]
+        out[a:b] = acc * torch.sigmoid(acc)
+        if taps > 1:
+            state[slot] = padded[padded.shape[0] - (taps - 1):].t()
+    return out
+
+
+def norm_mean_add_(stream, a, gain_a, b, gain_b, eps):
+    na = a * (a.pow(2).mean(-1, keepdim=True) + eps).rsqrt() * gain_a
+    nb = b * (b.pow(2).mean(-1, keepdim=True) + eps).rsqrt() * gain_b
+    stream += 0.5 * (na + nb)
+
+
+def moe_route(logits, correction, groups, keep, top, scale):
+    T, E = logits.shape
+    s = torch.sigmoid(logits.float())
+    choice = s + correction
+    if groups > 1 and keep < groups:
+        per = E // groups
+        grouped = choice.reshape(T, groups, per)
+        score = grouped.topk(min(2, per), dim=-1).values.sum(-1)
+        best = score.topk(keep, dim=-1).indices
+        allowed = torch.zeros((T, groups), dtype=torch.bool, device=logits.device)
+        allowed.scatter_(1, best, True)
+        choice = torch.where(allowed.repeat_interleave(per, dim=1), choice, torch.full_like(choice, float("-inf")))
+    idx = torch.sort(-choice, dim=-1, stable=True).indices[:, :top]
+    wts = s.gather(1, idx) * scale
+    dense = torch.zeros((T, E), dtype=torch.float32, device=logits.device)
+    dense.scatter_(1, idx, wts)
+    return dense, idx.int(), wts
+
+
+def moe_act(up, dense, ff, out_dtype):
+    T, N = up.shape
+    E = dense.shape[1]
+    w = torch.ones((T, N), dtype=torch.float32, device=up.device)
+    w[:, :E * ff] = dense.repeat_interleave(ff, dim=1)
+    return (torch.nn.functional.gelu(up.float()) * w).to(out_dtype)
 
 
 def latent_write(proj, off, rank, gain, eps, slot_mapping, cache):
@@ -184,7 +313,7 @@ def rope_kv_write(qkv, bias, positions, table, rotary_dim, nq, nkv, hd, slot_map
     return q
 
 
-def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window):
+def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, nq, nkv, hd, scale, window, block=None):
     T = q.shape[0]
     ps = k_cache.shape[2]
     out = torch.empty((T, nq, hd), dtype=torch.float32, device=q.device)
@@ -193,6 +322,8 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     for t in range(T):
         pos = int(positions[t])
         lo = max(0, pos - window + 1) if window else 0
+        if block:
+            lo = max(lo, pos // block * block)
         j = torch.arange(lo, pos + 1, device=q.device)
         pages = block_tables[int(seq_of_token[t])].long()[j // ps]
         k = k_cache[pages, :, j % ps, :].float()          # [n, nkv, hd]
@@ -205,10 +336,10 @@ def attention_simt(q, k_cache, v_cache, block_tables, positions, seq_of_token, n
     return out.reshape(T, nq * hd).to(q.dtype)
 
 
-def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window):
+def paged_attention(q, k_cache, v_cache, step, group, nq, nkv, hd, scale, window, block=None):
     g = step.groups[group]
     return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
-                          nq, nkv, hd, scale, window)
+                          nq, nkv, hd, scale, window, block)
 
 
 def gather_rows(x, rows):
@@ -257,6 +388,7 @@ def penalty_from_seen_(logits, seen, step, penalty):
     return logits
 
 
-ALL = ["add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
+ALL = ["gated_delta_rule", "gated_linear_attention", "qk_norm_rope_kv_write", "short_conv_silu", "norm_mean_add_", "moe_route", "moe_act",
+       "add_sinusoid_", "add_group_ssq", "group_norm_shift", "act_mul", "linear_act_mul", "tanh_cols", "delta_rule", "delta_out", "latent_write",
        "head_linear", "embed_gather", "add_rmsnorm", "linear", "can_accumulate", "linear_accumulate", "silu_mul", "linear_silu_mul", "rope_kv_write",
        "attention_simt", "paged_attention", "gather_rows", "sample_rows", "repetition_penalty_", "mark_seen", "penalty_from_seen_"]
