@@ -1,0 +1,658 @@
+"""The Nutopel design in the engine against the plain numpy statement of it (tests/plain/nutopel_plain.py).
+
+Every test makes its own small configuration and random weights.  Each body runs twice: with the PyTorch stand-ins
+for the kernels on the CPU (the parts, the cache manager, the batching), and on the GPU with the real kernels (marked
+``gpu``).  The configurations differ from one another in everything a configuration can say: key and value sizes that
+differ, one or several heads per key head, rotated channels from a few to all, with and without frequency scaling,
+blocks of positions smaller and larger than a page, convolutions of 2 to 5 taps, routers with and without groups,
+groups of one expert, layers without a shared expert and without a feed-forward.
+"""
+
+import json
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from tests import traces
+from tests.plain import nutopel_plain as plain
+
+
+def _moe(experts, top, ff, scale, groups=None, shared=None):
+    r = {"experts": experts, "top": top, "scale": scale}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    m = {"kind": "moe", "expert": {"ff": ff}, "router": r}
+    if shared:
+        m["shared"] = {"ff": shared}
+    return m
+
+
+def _pair(heads, kv, dim, vdim, size, rot, scale, right):
+    return {"left": {"heads": heads, "kv_heads": kv, "dim": dim, "vdim": vdim, "mask": {"size": size}, "rot": rot, "scale": scale},
+            "right": right}
+
+
+SCALED = {"base": 5000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 64, "fast": 16.0, "slow": 2.0}}
+CONFIG_A = {
+    "architecture": "Nutopel", "vocab": 300, "width": 80, "logit_scale": 0.7, "norm": {"eps": 1e-5},
+    "layers": [
+        {"type": "parallel", "mixer": _pair(4, 2, 24, 40, 20, SCALED, 0.3, {"heads": 4, "kv_heads": 2, "dim": 16, "vdim": 24, "conv": 3}),
+         "mlp": _moe(6, 3, 48, 1.7, groups=(3, 2), shared=56)},
+        {"type": "gla", "mixer": {"heads": 2, "dim": 24, "vdim": 40, "tau": 8.0, "decay_rank": 5}, "mlp": _moe(4, 1, 40, 0.8)},
+        {"type": "gla", "mixer": {"heads": 3, "dim": 16, "vdim": 16, "tau": 2.0, "decay_rank": 3}, "mlp": None},
+        {"type": "parallel", "mixer": _pair(2, 2, 32, 32, 33, {"base": 100.0, "dims": 32, "scaling": None}, 0.2,
+                                            {"heads": 1, "kv_heads": 1, "dim": 40, "vdim": 20, "conv": 2}),
+         "mlp": _moe(8, 2, 24, 1.0, groups=(4, 1), shared=32)},
+    ],
+}
+CONFIG_B = {          # heads of 64 on pages of 16: the tensor-core attention forms on the GPU (bfloat16); blocks of 50 positions
+    "architecture": "Nutopel", "vocab": 200, "width": 128, "logit_scale": 1.0, "norm": {"eps": 1e-6},
+    "layers": [
+        {"type": "gla", "mixer": {"heads": 1, "dim": 64, "vdim": 48, "tau": 4.0, "decay_rank": 8}, "mlp": _moe(4, 2, 64, 2.0, groups=(2, 1))},
+        {"type": "parallel", "mixer": _pair(6, 3, 64, 64, 50, {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 40, "fast": 8.0, "slow": 1.0}},
+                                            0.125, {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 32, "conv": 4}), "mlp": _moe(4, 2, 64, 2.0, shared=64)},
+        {"type": "parallel", "mixer": _pair(8, 8, 16, 16, 7, {"base": 10000.0, "dims": 8, "scaling": None}, 0.25,
+                                            {"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 4}), "mlp": None},
+    ],
+}
+ODD = {               # sizes that are multiples of nothing; groups of one expert; five taps
+    "architecture": "Nutopel", "vocab": 77, "width": 50, "logit_scale": 1.3, "norm": {"eps": 1e-4},
+    "layers": [
+        {"type": "parallel", "mixer": _pair(3, 1, 10, 14, 9, {"base": 50.0, "dims": 6, "scaling": {"factor": 1.5, "original": 16, "fast": 4.0, "slow": 0.5}},
+                                            0.4, {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 10, "conv": 5}), "mlp": _moe(5, 2, 18, 1.1, groups=(5, 3), shared=22)},
+        {"type": "gla", "mixer": {"heads": 5, "dim": 6, "vdim": 10, "tau": 16.0, "decay_rank": 2}, "mlp": _moe(3, 3, 14, 0.5)},
+    ],
+}
+ONLY_GLA = {"architecture": "Nutopel", "vocab": 90, "width": 64, "logit_scale": 2.0, "norm": {"eps": 1e-6},
+            "layers": [{"type": "gla", "mixer": {"heads": 2, "dim": 32, "vdim": 24, "tau": 1.0, "decay_rank": 4}, "mlp": None}]}
+CONFIGS = {"A": (CONFIG_A, 16), "B": (CONFIG_B, 16), "odd": (ODD, 8), "only_gla": (ONLY_GLA, 4)}
+
+
+def _devices():
+    return [pytest.param("cpu", id="stand-in"), pytest.param("cuda:0", id="gpu", marks=pytest.mark.gpu)]
+
+
+@pytest.fixture(params=_devices())
+def dev(request):
+    if request.param == "cpu":
+        request.getfixturevalue("cpu_ops")
+    elif not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    return request.param
+
+
+def make_model(tmp_path, config, seed=5, name="m", edit=None, std=0.12):
+    from sllm_b200.weights import SafetensorsFile, write_random_model, write_safetensors
+    d = write_random_model(os.path.join(str(tmp_path), name), config, seed, std=std, bias_std=0.4, gain_std=0.2)
+    if edit is not None:
+        f = SafetensorsFile(os.path.join(d, "model.safetensors"))
+        t = {n: f.tensor(n).float() for n in f.names()}
+        edit(t)
+        del f
+        write_safetensors(os.path.join(d, "model.safetensors"), {n: v.to(torch.bfloat16) for n, v in t.items()})
+    return d
+
+
+def plain_logits(d, reqs):
+    cfg, w = plain.load_model(d)
+    return {r: plain.forward(ids, cfg, w).astype(np.float32) for r, ids in reqs.items()}
+
+
+def compare(tr, out, want, dtype, what):
+    """float32: every logit to 3e-4.  bfloat16: the difference of a row (mean taken off, root mean square over the
+    vocabulary) relative to the row's own spread is rounding's: under 3 % for 19 rows in 20 and under 10 % for every
+    row (a lost key, state or expert moves rows by tens of per cent)."""
+    if dtype == "float32":
+        return traces.compare(tr, out, want, what=what, rtol=3e-4, atol=3e-4)
+    errs = []
+    for s in tr.steps:
+        for row, (req, pos) in enumerate(s["expect"]):
+            ref, got = want[req][pos], out[s["step"]][row]
+            d, r = got - ref, ref - ref.mean()
+            e = float(np.sqrt(((d - d.mean()) ** 2).mean()) / np.sqrt((r ** 2).mean()))
+            assert e < 0.10, f"{what}: step {s['step']}, request {req!r}, position {pos}: relative difference {e:.3g}"
+            errs.append(e)
+    assert np.quantile(errs, 0.95) < 0.03, f"{what}: 95th percentile of the rows' relative difference {np.quantile(errs, 0.95):.3g}"
+
+
+def dtypes_on(dev):
+    return ("float32",) if dev == "cpu" else ("float32", "bfloat16")
+
+
+def _requests(vocab, lengths, seed=3):
+    rng = np.random.default_rng(seed)
+    return {f"r{i}": rng.integers(0, vocab, n).tolist() for i, n in enumerate(lengths)}
+
+
+def _to(dev):
+    return lambda a: torch.from_numpy(np.ascontiguousarray(a, dtype=np.float32)).to(dev).contiguous()
+
+
+def _step(dev, q_lens, slots, ctx_lens=None, group=None):
+    """A batch description by hand: portions of ``q_lens`` tokens that end at ``ctx_lens`` (default: start at 0)."""
+    from sllm_b200.parts import StepContext
+    i32 = lambda v: torch.tensor(v, dtype=torch.int32, device=dev)
+    ctx_lens = list(ctx_lens or q_lens)
+    starts = np.concatenate([[0], np.cumsum(q_lens)])
+    pos = np.concatenate([np.arange(c - q, c) for q, c in zip(q_lens, ctx_lens)])
+    return StepContext(num_tokens=int(starts[-1]), num_seqs=len(q_lens), token_ids=i32([0] * int(starts[-1])), positions=i32(pos.tolist()),
+                       seq_of_token=i32(np.repeat(np.arange(len(q_lens)), q_lens).tolist()), q_start=i32(starts.tolist()),
+                       ctx_len=i32(ctx_lens), state_slots=i32(slots), logit_rows=i32([]), groups=[group] if group else [],
+                       q_lens=list(q_lens), ctx_lens=ctx_lens, max_q_len=max(q_lens), max_ctx_len=max(ctx_lens))
+
+
+# ---- configuration, plan, weights ---------------------------------------------------------------------------
+
+def test_config_plan_and_cache_needs():
+    from sllm_b200.config import ConfigError, architecture_of
+    from sllm_b200.models.causal_lm import CausalLM
+    from sllm_b200.parts import PagedKV, SlotState
+    arch = architecture_of(CONFIG_A)
+    cfg = arch.config_cls.from_dict(CONFIG_A)
+    assert cfg.to_dict() == CONFIG_A
+    p = arch.plan(cfg)
+    assert len(p.layers) == 4 and [e.layer for e in p.run_list] == [0, 1, 2, 3] and p.position is None
+    assert "ffn" not in p.layers[2].parts and p.final_norm.params["gain_scale"] == 0.7
+    m = CausalLM(p, dtype=torch.float32, device="cpu")
+    needs = [n for _, n in m.cache_needs()]
+    assert needs[0] == (PagedKV(2, 40, None), SlotState((4, 16, 24), "delta"), SlotState((2 * 32 + 96, 2), "conv"))
+    assert needs[1] == SlotState((2, 24, 40), "gla")
+    assert needs[3] == (PagedKV(2, 32, None), SlotState((1, 40, 20), "delta"), SlotState((100, 1), "conv"))
+    names = {s.name for s in m.tensor_specs()}
+    assert {"embed", "head", "final.norm", "l0.norm1", "l0.norm2", "l0.mix.left.q.norm", "l0.mix.right.v.conv", "l0.mix.right.A_log",
+            "l0.mix.left.out", "l0.mlp.e5.down", "l0.mlp.shared.up", "l0.mlp.correction", "l1.mix.a2.b", "l3.mix.right.dt_bias"} <= names
+    assert not any(n.startswith("l2.mlp") or n.startswith("l2.norm2") or n.startswith("l1.mlp.shared") for n in names)
+    bad_router = json.loads(json.dumps(CONFIG_A))
+    bad_router["layers"][0]["mlp"]["router"]["top"] = 5            # two groups of two experts cannot give five
+    bad_heads = json.loads(json.dumps(CONFIG_A))
+    bad_heads["layers"][0]["mixer"]["left"]["kv_heads"] = 3
+    for bad in (bad_router, bad_heads, dict(CONFIG_A, layers=[dict(CONFIG_A["layers"][1], type="other")]),
+                {k: v for k, v in CONFIG_A.items() if k != "norm"}, dict(CONFIG_A, layers=[])):
+        with pytest.raises(ConfigError):
+            arch.config_cls.from_dict(bad)
+
+
+def test_decay_rank_comes_from_the_checkpoint(tmp_path):
+    from sllm_b200.engine import build_model
+    d = make_model(tmp_path, CONFIG_A)
+    with open(os.path.join(d, "config.json")) as f:
+        raw = json.load(f)
+    for layer in raw["layers"]:
+        layer["mixer"].pop("decay_rank", None)
+    with open(os.path.join(d, "config.json"), "w") as f:
+        json.dump(raw, f)
+    model, _ = build_model(d, "float32", "cpu")
+    assert model.layers[1].mixer.rank == 5 and model.layers[2].mixer.rank == 3
+
+
+# ---- each mechanism alone: an operation or a part against the plain function ------------------------------------------
+
+def test_norm_with_a_gain_stored_around_zero(dev):
+    from sllm_b200.config.plan import PartSpec
+    from sllm_b200.parts import NORMS
+    rng = np.random.default_rng(0)
+    x, w = rng.standard_normal((9, 70)) * 3, rng.standard_normal(70) * 0.3
+    norm = NORMS.build(PartSpec("group_rmsnorm", {"size": 70, "groups": 1, "eps": 1e-3, "offset": 1.0, "gain_scale": 0.25}),
+                       dtype=torch.float32, device=dev)
+    norm.bind(lambda rel: torch.from_numpy(w.astype(np.float32)))
+    stream, pending = _to(dev)(x), _to(dev)(x[::-1].copy())
+    got = norm.add_norm(stream, pending).cpu().numpy()
+    np.testing.assert_allclose(got, plain.norm_one_plus(x + x[::-1], w, 1e-3) * 0.25, rtol=2e-5, atol=2e-5)
+    np.testing.assert_allclose(stream.cpu().numpy(), x + x[::-1], rtol=1e-6, atol=1e-6)
+
+
+@pytest.mark.parametrize("rot", [SCALED, {"base": 100.0, "dims": 32, "scaling": None},
+                                 {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 40, "fast": 8.0, "slow": 1.0}},
+                                 {"base": 50.0, "dims": 6, "scaling": {"factor": 1.5, "original": 16, "fast": 4.0, "slow": 0.5}}])
+def test_rotary_frequencies_with_two_regimes(rot):
+    from sllm_b200.parts.standard import Rotary
+    f, mag = Rotary.frequencies(rot["base"], rot["dims"], rot["scaling"])
+    pf, pmag = plain.rotary_frequencies(rot)
+    np.testing.assert_allclose(f, pf, rtol=1e-12)
+    assert abs(mag - pmag) < 1e-12
+    if rot["scaling"]:
+        plainf = rot["base"] ** (-2.0 * np.arange(rot["dims"] // 2) / rot["dims"])
+        assert f[0] == plainf[0] or rot["dims"] <= 6          # the fastest channel stays as it is
+        assert np.isclose(f[-1], plainf[-1] / rot["scaling"]["factor"])      # the slowest is stretched by the whole factor
+
+
+@pytest.mark.parametrize("nq,nkv,dim,vdim,D,rot", [(4, 2, 24, 40, 40, SCALED), (3, 1, 10, 14, 16, {"base": 50.0, "dims": 6, "scaling": None}),
+                                                   (2, 2, 32, 32, 32, {"base": 100.0, "dims": 32, "scaling": None}), (2, 1, 12, 8, 12, None)])
+def test_head_norms_rotation_and_the_cache_write(dev, nq, nkv, dim, vdim, D, rot):
+    import sllm_b200.ops as ops
+    from sllm_b200.parts.side_by_side import rotary_for
+    rng = np.random.default_rng(dim)
+    T, ps, pages = 23, 4, 12
+    x = rng.standard_normal((T, (nq + nkv) * dim + nkv * vdim + 3))           # (three columns more than the kernel reads)
+    gq, gk = 1 + 0.3 * rng.standard_normal(dim), 1 + 0.3 * rng.standard_normal(dim)
+    pos = rng.integers(0, 500, T)
+    slots = rng.permutation(pages * ps)[:T].astype(np.int32)
+    slots[4] = -1
+    to = _to(dev)
+    kc, vc = (torch.full((pages, nkv, ps, D), 7.0, dtype=torch.float32, device=dev) for _ in range(2))
+    table = rotary_for({"theta": rot["base"], "rotary_dim": rot["dims"], "scaling": rot["scaling"], "max_positions": 512},
+                       torch.float32, dev).table if rot else None
+    q = ops.qk_norm_rope_kv_write(to(x), to(gq), to(gk), 1e-5, torch.from_numpy(pos.astype(np.int32)).to(dev), table,
+                                  rot["dims"] if rot else 0, nq, nkv, dim, vdim, torch.from_numpy(slots).to(dev), kc, vc, torch.float32)
+    qk = x[:, :(nq + nkv) * dim].reshape(T, nq + nkv, dim)
+    wq = plain.norm_plain(qk[:, :nq], gq, 1e-5)
+    wk = plain.norm_plain(qk[:, nq:], gk, 1e-5)
+    if rot:
+        wq, wk = plain.rotate(wq, pos, rot), plain.rotate(wk, pos, rot)
+    wv = x[:, (nq + nkv) * dim:(nq + nkv) * dim + nkv * vdim].reshape(T, nkv, vdim)
+    got = q.cpu().numpy().reshape(T, nq, D)
+    np.testing.assert_allclose(got[..., :dim], wq, rtol=3e-5, atol=3e-5)
+    assert not got[..., dim:].any()
+    kf, vf = (c.cpu().numpy().transpose(0, 2, 1, 3).reshape(pages * ps, nkv, D) for c in (kc, vc))
+    keep = slots >= 0
+    np.testing.assert_allclose(kf[slots[keep]][..., :dim], wk[keep], rtol=3e-5, atol=3e-5)
+    np.testing.assert_allclose(vf[slots[keep]][..., :vdim], wv[keep], rtol=1e-6, atol=1e-6)
+    assert not kf[slots[keep]][..., dim:].any() and not vf[slots[keep]][..., vdim:].any()
+    untouched = np.setdiff1d(np.arange(pages * ps), slots[keep])
+    assert (kf[untouched] == 7.0).all() and (vf[untouched] == 7.0).all()      # the padding row wrote nothing
+
+
+def _paged(dev, dtype, nkv, D, ps, lens, rng):
+    """Caches filled with random keys and values for requests of ``lens`` tokens on scattered pages."""
+    from sllm_b200.parts import GroupView
+    per = [-(-n // ps) for n in lens]
+    order = rng.permutation(sum(per) + 3)
+    tables = np.full((len(lens), max(per) + 1), -1, dtype=np.int32)
+    at = 0
+    for s, n in enumerate(per):
+        tables[s, :n] = order[at:at + n]
+        at += n
+    k = rng.standard_normal((sum(per) + 3, nkv, ps, D)).astype(np.float32)
+    v = rng.standard_normal((sum(per) + 3, nkv, ps, D)).astype(np.float32)
+    g = GroupView(ps, torch.from_numpy(tables).to(dev), torch.zeros(1, dtype=torch.int32, device=dev))
+    return k, v, tables, g
+
+
+@pytest.mark.parametrize("hd,block,ps,dtype", [(24, 20, 4, "float32"), (64, 50, 16, "bfloat16"), (32, 33, 8, "bfloat16"), (16, 7, 16, "bfloat16"),
+                                               (64, 120, 16, "bfloat16"), (128, 64, 32, "bfloat16")])
+def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype):
+    """Prompt portions and single decoded tokens whose positions lie at the start, the end and the middle of a block of
+    positions, hundreds of tokens into a request.  The key just before the block's start is made to stand out (a copy of
+    the query, scaled): were it visible, it would take the whole softmax."""
+    import sllm_b200.ops as ops
+    if dev == "cpu" and dtype != "float32":
+        pytest.skip("the stand-ins are float32")
+    rng = np.random.default_rng(block)
+    nq, nkv, scale = 4, 2, 0.3
+    # (portion length, context after it): decoded tokens on a block's first and last position, in its middle and one beyond
+    # a page border; portions that start before a block's edge and end behind it, and one inside one block
+    cases = [(1, 3 * block + 1), (1, 4 * block), (1, 2 * block + block // 2), (1, 5 * block + 2), (block + 3, 2 * block + 2),
+             (5, 3 * block + 3), (2, block + 1), (3, block - 1 if block > 4 else 3), (2 * block + 1, 6 * block)]
+    q_lens, ctx = [c[0] for c in cases], [c[1] for c in cases]
+    k, v, tables, g = _paged(dev, dtype, nkv, hd, ps, ctx, rng)
+    T = sum(q_lens)
+    q = rng.standard_normal((T, nq, hd)).astype(np.float32)
+    step = _step(dev, q_lens, list(range(len(cases))), ctx, g)
+    pos, seq = step.positions.cpu().numpy(), step.seq_of_token.cpu().numpy()
+    for t in range(T):                       # the standing-out key right before each query's block, for the query's first head
+        j = pos[t] // block * block - 1
+        if j >= 0:
+            page = tables[seq[t], j // ps]
+            k[page, 0, j % ps] = q[t, 0] * 6.0
+    td = torch.float32 if dtype == "float32" else torch.bfloat16
+    qd, kd, vd = (torch.from_numpy(a).to(dev).to(td).contiguous() for a in (q.reshape(T, nq * hd), k, v))
+    got = ops.paged_attention(qd, kd, vd, step, 0, nq, nkv, hd, scale, None, block).float().cpu().numpy().reshape(T, nq, hd)
+    qf, kf, vf = qd.float().cpu().numpy().reshape(T, nq, hd).astype(np.float64), kd.float().cpu().numpy().astype(np.float64), vd.float().cpu().numpy().astype(np.float64)
+    for t in range(T):
+        lo = pos[t] // block * block
+        js = np.arange(lo, pos[t] + 1)
+        pages = tables[seq[t], js // ps]
+        for h in range(nq):
+            kk, vv = kf[pages, h // 2, js % ps], vf[pages, h // 2, js % ps]
+            s = kk @ qf[t, h] * scale
+            e = np.exp(s - s.max())
+            want = (e / e.sum()) @ vv
+            tol = 2e-5 if dtype == "float32" else 3e-2
+            np.testing.assert_allclose(got[t, h], want, rtol=tol, atol=tol, err_msg=f"token {t} (position {pos[t]}), head {h}")
+
+
+@pytest.mark.parametrize("C,taps", [(10, 2), (70, 3), (300, 4), (33, 5), (8, 1)])
+def test_short_convolution_across_portions_and_slots(dev, C, taps):
+    """Two requests side by side in portions down to one token (shorter than the taps), continuing from their state rows;
+    a third row of the state stays untouched."""
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(C)
+    lens = {0: 29, 1: 17}
+    off, ld = 3, C + 5
+    xs = {s: rng.standard_normal((n, ld)) for s, n in lens.items()}
+    w = rng.standard_normal((C, taps))
+    want = {s: plain.silu(plain.short_convolution(x[:, off:off + C], w)) for s, x in xs.items()}
+    to = _to(dev)
+    state = torch.zeros((3, C, max(taps - 1, 1)), dtype=torch.float32, device=dev)[:, :, :taps - 1].contiguous() if taps > 1 else None
+    slots, at, got = {0: 2, 1: 0}, {0: 0, 1: 0}, {0: [], 1: []}
+    for cut in [(1, 2), (1, 1), (2, 1), (9, 6), (1, 1), (3, 2), (20, 20)]:
+        live = [s for s in lens if at[s] < lens[s]]
+        q = [min(cut[s], lens[s] - at[s]) for s in live]
+        x = np.concatenate([xs[s][at[s]:at[s] + n] for s, n in zip(live, q)])
+        y = ops.short_conv_silu(to(x), off, to(w), state, _step(dev, q, [slots[s] for s in live])).cpu().numpy()
+        r0 = 0
+        for s, n in zip(live, q):
+            got[s].append(y[r0:r0 + n])
+            r0 += n
+            at[s] += n
+    for s in lens:
+        np.testing.assert_allclose(np.concatenate(got[s]), want[s], rtol=2e-5, atol=2e-5)
+        if taps > 1:
+            np.testing.assert_allclose(state[slots[s]].cpu().numpy(), xs[s][-(taps - 1):, off:off + C].T, rtol=1e-6)
+    assert taps == 1 or float(state[1].abs().max()) == 0.0
+
+
+def _portions(dev, lens, slots, cuts, run):
+    """Feed requests of ``lens`` tokens side by side in portions ``cuts``; ``run(rows by request, step) -> [T, ...]``."""
+    at, got = {s: 0 for s in lens}, {s: [] for s in lens}
+    for cut in cuts:
+        live = [s for s in lens if at[s] < lens[s]]
+        q = [min(cut[s], lens[s] - at[s]) for s in live]
+        y = run([(s, at[s], at[s] + n) for s, n in zip(live, q)], _step(dev, q, [slots[s] for s in live]))
+        r0 = 0
+        for s, n in zip(live, q):
+            got[s].append(y[r0:r0 + n])
+            r0 += n
+            at[s] += n
+    assert all(at[s] == lens[s] for s in lens)
+    return {s: np.concatenate(got[s]) for s in lens}
+
+
+CUTS = [(17, 1), (1, 2), (2, 9), (13, 1), (1, 1), (40, 40)]
+
+
+@pytest.mark.parametrize("heads,kv,dk,dv", [(1, 1, 64, 64), (4, 2, 16, 24), (3, 3, 40, 20), (6, 1, 12, 10), (80, 40, 16, 16), (2, 1, 130, 8)])
+def test_gated_delta_rule_in_portions_and_slots(dev, heads, kv, dk, dv):
+    """The mixer's recurrence with its convolutions, through the part's own `mix`: two requests in portions down to one
+    token against the whole sequences through the plain function.  80 heads fill the device (the kernel's wide form)."""
+    from sllm_b200.config.plan import PartSpec
+    from sllm_b200.parts import MIXERS, LayerCache
+    rng = np.random.default_rng(dk + heads)
+    W, taps, eps = 48, 3, 1e-5
+    K, V = kv * dk, heads * dv
+    w = {"m.q": rng.standard_normal((K, W)) * 0.3, "m.k": rng.standard_normal((K, W)) * 0.3, "m.v": rng.standard_normal((V, W)) * 0.3,
+         "m.q.conv": rng.standard_normal((K, taps)) * 0.6, "m.k.conv": rng.standard_normal((K, taps)) * 0.6, "m.v.conv": rng.standard_normal((V, taps)) * 0.6,
+         "m.b": rng.standard_normal((heads, W)) * 0.3, "m.a": rng.standard_normal((heads, W)) * 0.3, "m.A_log": rng.standard_normal(heads) * 0.5 - 2.0,
+         "m.dt_bias": rng.standard_normal(heads) * 0.5, "m.norm": 1 + 0.2 * rng.standard_normal(dv), "m.g": rng.standard_normal((V, W)) * 0.3,
+         "m.o": rng.standard_normal((W, V)) * 0.2}
+    w = {n: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64) for n, a in w.items()}
+    mixer = MIXERS.build(PartSpec("gated_delta", {"hidden_size": W, "heads": heads, "kv_heads": kv, "dim": dk, "vdim": dv, "conv": taps, "eps": eps}),
+                         dtype=torch.float32, device=dev)
+    mixer.bind(lambda rel: torch.from_numpy(w["m." + rel].astype(np.float32)))
+    lens, slots = {0: 37, 1: 21}, {0: 2, 1: 0}
+    xs = {s: rng.standard_normal((n, W)) for s, n in lens.items()}
+    want = {s: plain.gated_delta(x, w, "m.", {"heads": heads, "kv_heads": kv, "dim": dk, "vdim": dv}, eps) for s, x in xs.items()}
+    cache = LayerCache(states={"delta": torch.zeros((3, heads, dk, dv), dtype=torch.float32, device=dev),
+                               "conv": torch.zeros((3, 2 * K + V, taps - 1), dtype=torch.float32, device=dev)})
+    to = _to(dev)
+
+    def run(rows, step):
+        x = to(np.concatenate([xs[s][a:b] for s, a, b in rows]))
+        return mixer.out(mixer.mix(x, step, cache), torch.float32).cpu().numpy()
+    got = _portions(dev, lens, slots, CUTS, run)
+    for s in lens:
+        np.testing.assert_allclose(got[s], want[s], rtol=5e-4, atol=5e-4)
+    assert float(cache.states["delta"][1].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("heads,dk,dv,tau", [(1, 64, 48, 4.0), (2, 24, 40, 8.0), (5, 6, 10, 16.0), (90, 16, 16, 1.0), (2, 130, 12, 2.0)])
+def test_gated_linear_attention_in_portions_and_slots(dev, heads, dk, dv, tau):
+    from sllm_b200.config.plan import PartSpec
+    from sllm_b200.parts import MIXERS, LayerCache
+    rng = np.random.default_rng(dk + heads)
+    W, R, eps = 40, 3, 1e-5
+    K, V = heads * dk, heads * dv
+    w = {"m.q": rng.standard_normal((K, W)) * 0.3, "m.k": rng.standard_normal((K, W)) * 0.3, "m.v": rng.standard_normal((V, W)) * 0.3,
+         "m.g": rng.standard_normal((V, W)) * 0.3, "m.o": rng.standard_normal((W, V)) * 0.2, "m.norm": 1 + 0.2 * rng.standard_normal(dv),
+         "m.a1": rng.standard_normal((R, W)) * 0.5, "m.a2": rng.standard_normal((K, R)), "m.a2.b": rng.standard_normal(K) + 2.0}
+    w = {n: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64) for n, a in w.items()}
+    mixer = MIXERS.build(PartSpec("gated_linear_attention", {"hidden_size": W, "heads": heads, "dim": dk, "vdim": dv, "tau": tau, "eps": eps}),
+                         dtype=torch.float32, device=dev)
+    mixer.bind(lambda rel: torch.from_numpy(w["m." + rel].astype(np.float32)))
+    assert mixer.rank == R
+    lens, slots = {0: 37, 1: 21}, {0: 1, 1: 2}
+    xs = {s: rng.standard_normal((n, W)) for s, n in lens.items()}
+    want = {s: plain.gated_linear_attention(x, w, "m.", {"heads": heads, "dim": dk, "vdim": dv, "tau": tau}, eps) for s, x in xs.items()}
+    cache = LayerCache(states={"gla": torch.zeros((3, heads, dk, dv), dtype=torch.float32, device=dev)})
+    to = _to(dev)
+
+    def run(rows, step):
+        x = to(np.concatenate([xs[s][a:b] for s, a, b in rows]))
+        return mixer.out(mixer.mix(x, step, cache), torch.float32).cpu().numpy()
+    got = _portions(dev, lens, slots, CUTS, run)
+    for s in lens:
+        np.testing.assert_allclose(got[s], want[s], rtol=5e-4, atol=5e-4)
+    assert float(cache.states["gla"][0].abs().max()) == 0.0
+
+
+@pytest.mark.parametrize("E,top,groups,scale", [(6, 3, (3, 2), 1.7), (8, 2, (4, 1), 1.0), (4, 1, None, 0.8), (5, 2, (5, 3), 1.1), (3, 3, None, 0.5),
+                                                (64, 6, (8, 3), 2.5), (16, 4, (2, 2), 1.0)])
+def test_router_chooses_within_the_best_groups(dev, E, top, groups, scale):
+    """The router's kernel against the plain function, with corrections large enough to change the choice (some negative,
+    so that an excluded expert's score of zero would win over an allowed one's)."""
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(E)
+    T, W = 50, 24
+    h, wr = rng.standard_normal((T, W)), rng.standard_normal((E, W)) * 0.5
+    corr = rng.standard_normal(E) * 0.5 - 0.7
+    r = {"experts": E, "top": top, "scale": scale}
+    if groups:
+        r["groups"] = {"count": groups[0], "keep": groups[1]}
+    chosen, weight = plain.route(h, {"router": wr, "correction": corr}, "", r)
+    to = _to(dev)
+    dense, idx, wts = ops.moe_route(to(h @ wr.T), to(corr), groups[0] if groups else 1, groups[1] if groups else 1, top, scale)
+    want = np.zeros((T, E))
+    np.put_along_axis(want, chosen, weight, axis=1)
+    np.testing.assert_allclose(dense.cpu().numpy(), want, rtol=1e-5, atol=1e-6)
+    assert (np.sort(idx.cpu().numpy(), axis=1) == np.sort(chosen, axis=1)).all()
+    np.testing.assert_allclose(np.sort(wts.cpu().numpy(), axis=1), np.sort(weight, axis=1), rtol=1e-5)
+
+
+def test_mixture_of_experts_against_plain(dev):
+    from sllm_b200.config.plan import PartSpec
+    from sllm_b200.parts import FEED_FORWARDS
+    rng = np.random.default_rng(7)
+    for E, top, groups, ff, shared in ((6, 3, (3, 2), 20, 28), (4, 1, None, 17, 0), (8, 2, (4, 1), 8, 8)):
+        W, T = 36, 41
+        mlp = _moe(E, top, ff, 1.3, groups=groups, shared=shared)
+        w = {"router": rng.standard_normal((E, W)) * 0.5, "correction": rng.standard_normal(E) * 0.3}
+        for n in [f"e{e}" for e in range(E)] + (["shared"] if shared else []):
+            f = shared if n == "shared" else ff
+            w[f"{n}.up"], w[f"{n}.down"] = rng.standard_normal((f, W)) * 0.4, rng.standard_normal((W, f)) * 0.4
+        w = {n: torch.from_numpy(a.astype(np.float32)).to(torch.bfloat16).float().numpy().astype(np.float64) for n, a in w.items()}
+        part = FEED_FORWARDS.build(PartSpec("routed_experts", {"hidden_size": W, "experts": E, "top": top, "groups": groups[0] if groups else 1,
+                                                              "keep": groups[1] if groups else 1, "scale": 1.3, "expert_ff": ff, "shared_ff": shared}),
+                                   dtype=torch.float32, device=dev)
+        part.bind(lambda rel: torch.from_numpy(w[rel].astype(np.float32)))
+        h = rng.standard_normal((T, W))
+        stream = torch.zeros((T, W), dtype=torch.float32, device=dev)
+        term = part.forward(_to(dev)(h), None, residual=stream)
+        got = stream.cpu().numpy() + (0 if term is None else (term.sum(0) if term.dim() == 3 else term).cpu().numpy())
+        np.testing.assert_allclose(got, plain.mixture(h, w, "", mlp), rtol=3e-4, atol=3e-4)
+
+
+def test_normed_mean_of_two_outputs(dev):
+    import sllm_b200.ops as ops
+    rng = np.random.default_rng(3)
+    T, W = 11, 70
+    x, a, b = rng.standard_normal((T, W)), rng.standard_normal((T, W)) * 5, rng.standard_normal((T, W)) * 0.01
+    ga, gb = 1 + 0.3 * rng.standard_normal(W), 1 + 0.3 * rng.standard_normal(W)
+    to = _to(dev)
+    stream = to(x)
+    ops.norm_mean_add_(stream, to(a), to(ga), to(b), to(gb), 1e-4)
+    want = x + 0.5 * (plain.norm_plain(a, ga, 1e-4) + plain.norm_plain(b, gb, 1e-4))
+    np.testing.assert_allclose(stream.cpu().numpy(), want, rtol=2e-5, atol=2e-5)
+
+
+# ---- the whole model through the engine: every cutting against the plain implementation ---------------------------
+
+@pytest.mark.parametrize("which", ["A", "B", "odd", "only_gla"])
+def test_every_cutting_against_plain(tmp_path, dev, which):
+    """Whole prompts; most of a prompt and the rest token by token; portions of changing size down to two tokens; up to
+    four requests at a time, portions beside single tokens.  The pools hold the trace's peak only and freed pages are
+    poisoned, so pages and state slots are used again and a read of a page no longer held would show."""
+    from sllm_b200.engine import Engine, build_model
+    config, page = CONFIGS[which]
+    d = make_model(tmp_path, config)
+    reqs = _requests(config["vocab"], (70, 37, 100, 1, 45, 64, 23))
+    want = plain_logits(d, reqs)
+    for dtype in dtypes_on(dev):
+        model, _ = build_model(d, dtype, dev)
+        for mode in ("whole", "tail_decode", "portions", "mixed"):
+            tr = getattr(traces, mode)(reqs)
+            eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=4, poison_freed=True)
+            out = traces.replay_engine(tr, eng)
+            compare(tr, out, want, dtype, f"{which}/{dtype}/{mode}")
+            eng.cache.check()
+            assert not eng.cache.requests and all(g.pool.used_count == 0 for g in eng.cache.groups)
+            if mode == "mixed" and eng.cache.groups:
+                assert eng.cache.reuse_count > 0
+
+
+def test_batch_of_unequal_requests_equals_each_alone(tmp_path, dev):
+    from sllm_b200.engine import Engine, StepEntry, build_model
+    d = make_model(tmp_path, CONFIG_A)
+    reqs = _requests(CONFIG_A["vocab"], (33, 2, 19, 50), seed=8)
+    model, _ = build_model(d, "float32", dev)
+    alone = {}
+    for r, ids in reqs.items():
+        eng = Engine(model, page_size=16, num_pages=8, max_requests=2)
+        a = eng.step([StepEntry(r, ids[:-1], [len(ids) - 2])])
+        b = eng.step([StepEntry(r, ids[-1:], [0])])
+        alone[r] = torch.cat([a, b]).cpu().numpy()
+    eng = Engine(model, page_size=16, num_pages=16, max_requests=5)
+    eng.step([StepEntry("warm", [1, 2, 3], [])])            # takes slot 0 and the first page, then leaves
+    eng.finish("warm")
+    order = ["r3", "r1", "r0", "r2"]
+    a = eng.step([StepEntry(r, reqs[r][:-1], [len(reqs[r]) - 2]) for r in order]).cpu().numpy()
+    b = eng.step([StepEntry(r, reqs[r][-1:], [0]) for r in order]).cpu().numpy()
+    for i, r in enumerate(order):
+        np.testing.assert_allclose(np.stack([a[i], b[i]]), alone[r], rtol=2e-5, atol=2e-5)
+
+
+def _sharp(t):
+    """Attention that all but picks one key, recurrent states that all but never forget, and a router whose corrections
+    decide: with these a lost key, a dropped state or a wrong expert changes the logits by far more than the tolerance."""
+    for n in list(t):
+        if n.endswith("left.q"):
+            t[n] *= 6.0
+        if n.endswith("A_log"):
+            t[n] = t[n] * 0.1 - 5.0
+        if n.endswith("a2.b"):
+            t[n] = t[n] * 0.1 + 5.0
+        if n.endswith("mix.left.out"):
+            t[n] *= 2.0
+
+
+def test_keys_at_block_and_page_borders_and_a_long_memory(tmp_path, dev):
+    """Sharpened weights (`_sharp`): a prompt of several hundred tokens, cut at and beside page and block borders, then
+    decoded token by token across more of them; every position wanted."""
+    from sllm_b200.engine import Engine, build_model
+    config, page = CONFIG_B, 16
+    d = make_model(tmp_path, config, edit=_sharp, seed=11)
+    ids = _requests(config["vocab"], (260,), seed=12)["r0"]
+    cfg, w = plain.load_model(d)
+    full = plain.forward(ids, cfg, w)
+    cut = plain.forward(ids[150:], cfg, w)                  # the memory matters: without the first 150 tokens the end differs
+    assert np.abs(cut[-1] - full[-1]).max() > 0.05
+    want = {"r0": full.astype(np.float32)}
+    for dtype in dtypes_on(dev):
+        model, _ = build_model(d, dtype, dev)
+        tr = traces.Trace()
+        at = 0
+        for n in (15, 1, 1, 16, 15, 1, 1, 2, 47, 1, 2, 3, 25):     # up to, onto and over borders of pages (16) and of blocks (50)
+            tr.step([("r0", at, ids[at:at + n], range(n))])
+            at += n
+        while at < len(ids):
+            tr.step([("r0", at, ids[at:at + 1], [0])], end=["r0"] if at == len(ids) - 1 else [])
+            at += 1
+        eng = Engine(model, page_size=page, num_pages=tr.max_tokens // page, max_requests=1, poison_freed=True)
+        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"far/{dtype}")
+
+
+def test_long_decoding_from_a_short_prompt(tmp_path, dev):
+    """Three tokens of prompt, then 150 tokens one at a time: the states and the cache carry everything, across many pages
+    and blocks of positions; every step's logits against the plain implementation.  The first tokens of the sequence are
+    wanted too (the convolution's zeros before the start, the empty state)."""
+    from sllm_b200.engine import Engine, build_model
+    d = make_model(tmp_path, CONFIG_A, seed=41)
+    reqs = _requests(CONFIG_A["vocab"], (153,), seed=42)
+    want = plain_logits(d, reqs)
+    for dtype in dtypes_on(dev):
+        model, _ = build_model(d, dtype, dev)
+        tr = traces.tail_decode(reqs, tail=150)
+        eng = Engine(model, page_size=8, num_pages=tr.max_tokens // 8, max_requests=1)
+        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"long/{dtype}")
+        tr = traces.Trace()
+        tr.step([("r0", 0, reqs["r0"][:1], [0])])
+        tr.step([("r0", 1, reqs["r0"][1:2], [0])])
+        tr.step([("r0", 2, reqs["r0"][2:5], [0, 1, 2])], end=["r0"])
+        eng = Engine(model, page_size=8, num_pages=8, max_requests=1)
+        compare(tr, traces.replay_engine(tr, eng), want, dtype, f"first/{dtype}")
+
+
+def test_greedy_generation_through_the_entry_point(tmp_path, dev):
+    """`LLM.generate`: admission, the token budget, prompts in portions, decoding (from captured graphs on the GPU),
+    sampling on the device; against greedy decoding with the plain implementation."""
+    from sllm_b200.engine import build_model
+    from sllm_b200.engine.llm import LLM
+    from sllm_b200.sampling import SamplingParams
+    d = make_model(tmp_path, CONFIG_A, seed=21)
+    cfg, w = plain.load_model(d)
+    prompts = list(_requests(CONFIG_A["vocab"], (9, 40, 17, 3, 26), seed=22).values())
+    new = 10
+    model, _ = build_model(d, "float32", dev)
+    llm = LLM(model=model, block_size=16, num_pages=40, max_num_seqs=3, chunk_size=16, max_batch_tokens=48, max_model_len=128)
+    res = llm.generate(prompts, SamplingParams(max_new=new))
+    for pr, r in zip(prompts, res):
+        ids, out = list(pr), []
+        for _ in range(new):
+            logits = plain.forward(ids, cfg, w)[-1]
+            top = np.sort(logits)[-2:]
+            out.append(int(np.argmax(logits)))
+            ids.append(out[-1])
+            if top[1] - top[0] < 1e-3:      # a tie the rounding may break either way: compare up to here
+                break
+        assert r.ids[:len(out)] == out, (len(pr), r.ids, out)
+    llm.engine.cache.check()
+    assert not llm.engine.cache.requests
+
+
+def test_command_line_with_random_weights(tmp_path, capsys, dev, monkeypatch):
+    import sllm_b200.engine.llm as llm_mod
+    from sllm_b200.serving import main as cli
+    recipe = "tiny-nutopel"
+    if dev == "cpu":
+        import yaml
+        real = llm_mod.LLM
+        monkeypatch.setattr(llm_mod, "LLM", lambda model_dir, **kw: real(model_dir, **dict(kw, device="cpu")))
+        with open(os.path.join(cli.RECIPES_DIR, "tiny-nutopel.yaml")) as f:
+            raw = yaml.safe_load(f)
+        raw["memory"] = {"kv_device_bytes": 1 << 20}
+        recipe = os.path.join(str(tmp_path), "tiny-nutopel.yaml")
+        with open(recipe, "w") as f:
+            yaml.safe_dump(raw, f)
+    assert cli.main([recipe]) == 0
+    out = capsys.readouterr().out
+    assert "Nutopel: 3 layers" in out
+    assert cli.main([recipe, "--mode", "run", "--random-weights", "4", "--prompt-ids", "5,17,3,150,42", "--max-new", "5",
+                     "--dtype", "float32", "--log-level", "ERROR"]) == 0
+    got = [int(t) for t in capsys.readouterr().out.strip().split(",")]
+    assert len(got) == 5 and all(0 <= t < 280 for t in got)
+
+
+@pytest.mark.gpu
+def test_replay_program_on_a_model_folder(tmp_path):
+    """bin/trace_run as a user runs it: the model class chosen by config.json, all four cuttings in one trace, four state slots."""
+    if not torch.cuda.is_available():
+        pytest.skip("no CUDA device")
+    d = make_model(tmp_path, CONFIG_B, seed=31)
+    reqs = _requests(CONFIG_B["vocab"], (40, 75, 9, 120, 51), seed=32)
+    want = traces.tagged(plain_logits(d, reqs))
+    tr = traces.all_modes(reqs)
+    for dtype in ("float32", "bfloat16"):
+        out_dir = os.path.join(str(tmp_path), f"out_{dtype}")
+        out = traces.replay_subprocess(tr, d, dtype, out_dir, 16)
+        compare(tr, out, want, dtype, f"replay/{dtype}")
