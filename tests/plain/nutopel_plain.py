@@ -202,8 +202,10 @@ def gated_linear_attention(h, w, p, m, eps):
 
 # ---- feed-forward ------------------------------------------------------------------------------------
 
-def route(h, w, p, r):
-    """(chosen experts [T, top], their weights [T, top])."""
+def route(h, w, p, r, margins=None):
+    """(chosen experts [T, top], their weights [T, top]).  ``margins`` (a list) receives, per token, how far the choice
+    was from going another way: the smaller of the gaps between the last group kept and the first one left out, and
+    between the last expert chosen and the first one not."""
     E, top = int(r["experts"]), int(r["top"])
     s = sigmoid(h @ w[p + "router"].T)
     choice = s + w[p + "correction"][None, :]
@@ -214,10 +216,18 @@ def route(h, w, p, r):
         grouped = choice.reshape(-1, count, per)
         score = np.sort(grouped, axis=-1)[..., -2:].sum(-1)
         best = np.argsort(-score, axis=-1, kind="stable")[:, :keep]
+        ranked = -np.sort(-score, axis=-1)
+        group_gap = ranked[:, keep - 1] - ranked[:, keep] if keep < count else np.full(h.shape[0], np.inf)
         allowed = np.zeros((h.shape[0], count), dtype=bool)
         np.put_along_axis(allowed, best, True, axis=1)
         choice = np.where(np.repeat(allowed, per, axis=1), choice, -np.inf)
+    else:
+        group_gap = np.full(h.shape[0], np.inf)
     chosen = np.argsort(-choice, axis=-1, kind="stable")[:, :top]
+    if margins is not None:
+        ranked = -np.sort(-choice, axis=-1)
+        gap = ranked[:, top - 1] - ranked[:, top] if top < E else np.full(h.shape[0], np.inf)
+        margins.append(np.minimum(gap, group_gap))
     return chosen, np.take_along_axis(s, chosen, axis=1) * float(r["scale"])
 
 
@@ -225,8 +235,8 @@ def expert(h, w, p):
     return gelu_erf(h @ w[p + "up"].T) @ w[p + "down"].T
 
 
-def mixture(h, w, p, mlp):
-    chosen, weight = route(h, w, p, mlp["router"])
+def mixture(h, w, p, mlp, margins=None):
+    chosen, weight = route(h, w, p, mlp["router"], margins)
     out = np.zeros_like(h)
     for t in range(h.shape[0]):
         for e, g in zip(chosen[t], weight[t]):
@@ -238,8 +248,9 @@ def mixture(h, w, p, mlp):
 
 # ---- the model ------------------------------------------------------------------------------------
 
-def forward(ids, cfg, w, dtype=np.float64, layers_out=None):
-    """Logits [T, vocab] of one sequence; ``layers_out`` (a list) receives the stream after every layer."""
+def forward(ids, cfg, w, dtype=np.float64, layers_out=None, margins=None):
+    """Logits [T, vocab] of one sequence; ``layers_out`` (a list) receives the stream after every layer, ``margins`` (a
+    list) every router's margins per token (see `route`)."""
     eps = float(cfg["norm"]["eps"])
     positions = np.arange(len(ids))
     x = w["embed"][np.asarray(ids, dtype=np.int64)].astype(dtype)
@@ -253,7 +264,7 @@ def forward(ids, cfg, w, dtype=np.float64, layers_out=None):
         else:
             raise ValueError(layer["type"])
         if layer.get("mlp") is not None:
-            x = x + mixture(norm_one_plus(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"])
+            x = x + mixture(norm_one_plus(x, w[p + "norm2"], eps), w, p + "mlp.", layer["mlp"], margins)
         if layers_out is not None:
             layers_out.append(x.copy())
     return (norm_one_plus(x, w["final.norm"], eps) @ w["head"].T) * float(cfg["logit_scale"])
