@@ -407,18 +407,40 @@ def design_configs(sz: dict):
     return ours, qwen
 
 
+def nutopel_config(sz: dict) -> dict:
+    """Nutopel at one size: the same width, depth and vocabulary; layers alternate between gated linear attention (heads of
+    64 x 64, the state of the other design's recurrent heads) and the pair of block-local grouped-query attention (an eighth
+    of the heads as kv heads, blocks of 1,024 positions, half the head rotated) beside a gated delta rule (heads of 128 x 128
+    behind convolutions of four taps); the feed-forward is eight experts of a quarter of the dense size, two of them used, in
+    four groups of which two are kept, plus a shared expert of half the dense size (as many multiplications a token as the
+    dense feed-forward's two thirds)."""
+    W, H, D = sz["width"], sz["heads"], sz["dim"]
+    mlp = {"kind": "moe", "expert": {"ff": sz["ff"] // 4 // 64 * 64}, "shared": {"ff": sz["ff"] // 2 // 64 * 64},
+           "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
+    gla = {"type": "gla", "mixer": {"heads": W // 64, "dim": 64, "vdim": 64, "tau": 16.0, "decay_rank": 64}, "mlp": mlp}
+    left = {"heads": H, "kv_heads": max(1, H // 8), "dim": D, "vdim": D, "mask": {"size": 1024}, "scale": D ** -0.5,
+            "rot": {"base": 10000.0, "dims": D // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
+    right = {"heads": W // 128, "kv_heads": max(1, W // 256), "dim": 128, "vdim": 128, "conv": 4}
+    pair = {"type": "parallel", "mixer": {"left": left, "right": right}, "mlp": mlp}
+    return {"architecture": "Nutopel", "vocab": sz["vocab"], "width": W, "logit_scale": 1.0, "norm": {"eps": 1e-5},
+            "layers": [gla if i % 2 == 0 else pair for i in range(sz["layers"])]}
+
+
 def design_run(args) -> dict:
     global PREFILL_TOKENS
     import torch
 
     from sllm_b200.engine import build_random_model
     peaks, peaks_kind = load_peaks()
-    out = {"workload": "rososun", "dtype": "bfloat16", "data": "synthetic (random weights, uniform random token ids)",
+    out = {"workload": args.workload, "dtype": "bfloat16", "data": "synthetic (random weights, uniform random token ids)",
            "prefill_tokens": args.prefill_tokens, "decode": {"batch": args.batch, "context": args.context},
            "peaks": dict(peaks, kind=peaks_kind), "sizes": {}}
     for name, sz in DESIGN_SIZES.items():
         rec = {}
-        for which, config in zip(("rososun", "qwen2"), design_configs(sz)):
+        designs = list(zip(("rososun", "qwen2"), design_configs(sz)))
+        if args.workload == "nutopel":
+            designs.insert(0, ("nutopel", nutopel_config(sz)))
+        for which, config in designs:
             model, _ = build_random_model(config, seed=0, dtype="bfloat16", device="cuda:0", std=0.02)
             cfg = {"vocab_size": sz["vocab"]}
             torch.cuda.synchronize()
@@ -692,7 +714,7 @@ def base_config(cfg, args, prompt_len) -> dict:
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--workload", choices=("decode", "rososun") + tuple(SERVING), default="decode",
+    ap.add_argument("--workload", choices=("decode", "rososun", "nutopel") + tuple(SERVING), default="decode",
                     help="decode: the default run; serve-*: the baseline's serving workloads through LLM.generate")
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=32)
@@ -731,7 +753,7 @@ def main(argv=None) -> int:
     if not torch.cuda.is_available():
         print(json.dumps({"error": "no CUDA device"}))
         return 1
-    if args.workload == "rososun":
+    if args.workload in ("rososun", "nutopel"):
         print(json.dumps(design_run(args)))
         return 0
     if args.workload != "decode":

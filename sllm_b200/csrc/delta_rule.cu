@@ -223,20 +223,22 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         }
 #pragma unroll
         for (int cc = 0; cc < CB; ++cc) us[cc] = ut[cc] = o[cc] = o2[cc] = 0.f;
+        if (p.mode != 2) {          // (a recurrence without a removal has u = 0: nothing to sum)
 #pragma unroll
-        for (int n = 0; n < RPT; n += 2) {
-          const float ua = u[n * SPLIT], ub = u[(n + 1) * SPLIT];
+          for (int n = 0; n < RPT; n += 2) {
+            const float ua = u[n * SPLIT], ub = u[(n + 1) * SPLIT];
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+              us[cc] = fmaf(ua, s[n][cc], us[cc]);
+              ut[cc] = fmaf(ub, s[n + 1][cc], ut[cc]);
+            }
+          }
 #pragma unroll
           for (int cc = 0; cc < CB; ++cc) {
-            us[cc] = fmaf(ua, s[n][cc], us[cc]);
-            ut[cc] = fmaf(ub, s[n + 1][cc], ut[cc]);
+            us[cc] += ut[cc];
+#pragma unroll
+            for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
           }
-        }
-#pragma unroll
-        for (int cc = 0; cc < CB; ++cc) {
-          us[cc] += ut[cc];
-#pragma unroll
-          for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
         }
 #pragma unroll
         for (int n = 0; n < RPT; n += 2) {

@@ -111,6 +111,34 @@ moe_act_kernel(const TI* __restrict__ up, const float* __restrict__ dense, TO* _
   }
 }
 
+// The same for bfloat16 in and out, eight columns a thread (one 16-byte load and store): needs ff, N and the routed
+// experts' columns to be multiples of 8, so that a thread's columns share one expert.  The columns of an expert that a
+// token does not use are not read.
+__global__ void __launch_bounds__(256)
+moe_act_vec_kernel(const __nv_bfloat16* __restrict__ up, const float* __restrict__ dense, __nv_bfloat16* __restrict__ out, int N,
+                   int E, int ff) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  const int routed = E * ff;
+  for (int c = (blockIdx.y * blockDim.x + threadIdx.x) * 8; c < N; c += gridDim.y * blockDim.x * 8) {
+    const float w = c < routed ? dense[(size_t)t * E + c / ff] : 1.f;
+    uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+    if (w != 0.f) {
+      raw = *reinterpret_cast<const uint4*>(up + (size_t)t * N + c);
+      __nv_bfloat162* h2 = reinterpret_cast<__nv_bfloat162*>(&raw);
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        float2 z = __bfloat1622float2(h2[k]);
+        z.x = 0.5f * z.x * (1.0f + erff(z.x * 0.70710678118654752440f)) * w;
+        z.y = 0.5f * z.y * (1.0f + erff(z.y * 0.70710678118654752440f)) * w;
+        h2[k] = __floats2bfloat162_rn(z.x, z.y);
+      }
+    }
+    *reinterpret_cast<uint4*>(out + (size_t)t * N + c) = raw;
+  }
+}
+
 }  // namespace sllm
 
 using namespace sllm;
@@ -132,6 +160,14 @@ SLLM_EXPORT int sllm_moe_act(const void* up, int in_dtype, const float* dense, v
                              cudaStream_t stream) {
   SLLM_REQUIRE(T >= 0 && N >= 1 && E >= 0 && ff >= 1 && (long)E * ff <= N, "moe_act: bad sizes T=%d N=%d E=%d ff=%d", T, N, E, ff);
   if (T == 0) return SLLM_OK;
+  if (in_dtype == SLLM_BF16 && out_dtype == SLLM_BF16 && N % 8 == 0 && ff % 8 == 0 && (uintptr_t)up % 16 == 0 &&
+      (uintptr_t)out % 16 == 0) {
+    int by = (N / 8 + 255) / 256;
+    if (by > 64) by = 64;
+    launch_kernel(moe_act_vec_kernel, dim3((unsigned)T, (unsigned)by), 256, 0, stream, (const __nv_bfloat16*)up, dense,
+                  (__nv_bfloat16*)out, N, E, ff);
+    return launch_status("moe_act");
+  }
   int by = (N + 255) / 256;
   if (by > 64) by = 64;
   const dim3 grid((unsigned)T, (unsigned)by);
