@@ -42,15 +42,19 @@ def _check_mixer(i: int, typ: str, m: dict) -> None:
     for k in ("heads", "kv_heads", "dim", "vdim"):
         get_int(left, k), get_int(right, k)
     get_float(left, "scale")
-    get_int(_section(left, "mask", where + ".left"), "size")
-    rot = _section(left, "rot", where + ".left")
-    get_float(rot, "base"), get_int(rot, "dims", minimum=2)
-    sc = rot.get("scaling")
-    if sc is not None:
-        if not isinstance(sc, dict):
-            raise ConfigError(f"{where}.left.rot.scaling must be an object or null")
-        for k in ("factor", "original", "fast", "slow"):
-            get_float(sc, k)
+    if left.get("mask") is not None:                     # (no mask: every earlier position is seen)
+        get_int(_section(left, "mask", where + ".left"), "size")
+    if left.get("rot") is not None:                      # (no rot: queries and keys are not rotated)
+        rot = _section(left, "rot", where + ".left")
+        get_float(rot, "base")
+        if get_int(rot, "dims", minimum=2) % 2 or rot["dims"] > left["dim"]:
+            raise ConfigError(f"{where}.left.rot.dims={rot['dims']} must be even and at most dim={left['dim']}")
+        sc = rot.get("scaling")
+        if sc is not None:
+            if not isinstance(sc, dict):
+                raise ConfigError(f"{where}.left.rot.scaling must be an object or null")
+            for k in ("factor", "original", "fast", "slow"):
+                get_float(sc, k)
     get_int(right, "conv")
     for side, s in (("left", left), ("right", right)):
         if s["heads"] % s["kv_heads"]:
@@ -127,10 +131,10 @@ def _mixer_spec(cfg: NutopelConfig, l: LayerConfig) -> PartSpec:
         return PartSpec("gated_linear_attention", {"hidden_size": W, "heads": m["heads"], "dim": m["dim"], "vdim": m["vdim"],
                                                    "tau": m["tau"], "eps": eps, "decay_rank": m.get("decay_rank")})
     left, right = m["left"], m["right"]
-    rot = left["rot"]
+    rot, mask = left.get("rot"), left.get("mask")
     attention = {"hidden_size": W, "heads": left["heads"], "kv_heads": left["kv_heads"], "dim": left["dim"], "vdim": left["vdim"],
-                 "scale": left["scale"], "eps": eps, "block": left["mask"]["size"], "max_positions": MAX_POSITIONS,
-                 "rotary": {"theta": rot["base"], "rotary_dim": rot["dims"], "scaling": rot.get("scaling")}}
+                 "scale": left["scale"], "eps": eps, "block": mask["size"] if mask else None, "max_positions": MAX_POSITIONS,
+                 "rotary": {"theta": rot["base"], "rotary_dim": rot["dims"], "scaling": rot.get("scaling")} if rot else None}
     delta = {"hidden_size": W, "heads": right["heads"], "kv_heads": right["kv_heads"], "dim": right["dim"], "vdim": right["vdim"],
              "conv": right["conv"], "eps": eps}
     return PartSpec("side_by_side", {"hidden_size": W, "eps": eps, "left": {"kind": "normed_attention", "params": attention},

@@ -296,17 +296,19 @@ def _paged(dev, dtype, nkv, D, ps, lens, rng):
     return k, v, tables, g
 
 
-@pytest.mark.parametrize("hd,block,ps,dtype", [(24, 20, 4, "float32"), (64, 50, 16, "bfloat16"), (32, 33, 8, "bfloat16"), (16, 7, 16, "bfloat16"),
-                                               (64, 120, 16, "bfloat16"), (128, 64, 32, "bfloat16")])
-def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype):
+@pytest.mark.parametrize("hd,block,ps,dtype,nq,nkv", [(24, 20, 4, "float32", 4, 2), (64, 50, 16, "bfloat16", 4, 2), (32, 33, 8, "bfloat16", 4, 2),
+                                                      (16, 7, 16, "bfloat16", 4, 2), (64, 120, 16, "bfloat16", 6, 1), (128, 64, 32, "bfloat16", 4, 4),
+                                                      (64, 50, 16, "bfloat16", 24, 1), (40, 9, 8, "float32", 3, 1)])
+def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype, nq, nkv):
     """Prompt portions and single decoded tokens whose positions lie at the start, the end and the middle of a block of
     positions, hundreds of tokens into a request.  The key just before the block's start is made to stand out (a copy of
-    the query, scaled): were it visible, it would take the whole softmax."""
+    the query, scaled): were it visible, it would take the whole softmax.  24 heads on one key head are more rows a
+    decoded token than the decode form's tile: its tokens go through the prompt form."""
     import sllm_b200.ops as ops
     if dev == "cpu" and dtype != "float32":
         pytest.skip("the stand-ins are float32")
     rng = np.random.default_rng(block)
-    nq, nkv, scale = 4, 2, 0.3
+    scale, G = 0.3, nq // nkv
     # (portion length, context after it): decoded tokens on a block's first and last position, in its middle and one beyond
     # a page border; portions that start before a block's edge and end behind it, and one inside one block
     cases = [(1, 3 * block + 1), (1, 4 * block), (1, 2 * block + block // 2), (1, 5 * block + 2), (block + 3, 2 * block + 2),
@@ -331,7 +333,7 @@ def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype):
         js = np.arange(lo, pos[t] + 1)
         pages = tables[seq[t], js // ps]
         for h in range(nq):
-            kk, vv = kf[pages, h // 2, js % ps], vf[pages, h // 2, js % ps]
+            kk, vv = kf[pages, h // G, js % ps], vf[pages, h // G, js % ps]
             s = kk @ qf[t, h] * scale
             e = np.exp(s - s.max())
             want = (e / e.sum()) @ vv
