@@ -58,6 +58,11 @@ struct AttnTcParams {
   const __nv_bfloat16* q;        // [T, nq, HD]
   __nv_bfloat16* out;            // [T, nq, HD]
   const int* block_tables;       // [S, max_pages]
+  // A sequence of this launch may be a part of a request (a block of positions inside which attention is ordinary causal
+  // attention): then seq_row[seq] is the request's row of block_tables and page_shift[seq] the page its positions count from
+  // (q_start and ctx_len describe the part).  Both null: a sequence is a request.
+  const int* seq_row;            // [S] or null
+  const int* page_shift;         // [S] or null
   const int* q_start;            // [S+1]
   const int* ctx_len;            // [S]
   const int* tile_seq;           // [tiles]
@@ -212,7 +217,9 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
   }
   const int key_hi = RT == 1 ? key_end[0] : max(key_end[0], key_end[RT - 1]);
   const int n_tiles = RT == 1 ? n_of[0] : max(n_of[0], n_of[RT - 1]);
-  const int* bt = p.block_tables + (size_t)seq * p.max_pages;
+  const int page_shift = p.page_shift ? p.page_shift[seq] : 0;
+  const int* bt = p.block_tables + (size_t)(p.seq_row ? p.seq_row[seq] : seq) * p.max_pages + page_shift;
+  const int max_pages = p.max_pages - page_shift;
 
   if (warp == PRODUCER) {
     // ---------------- TMA producer ----------------
@@ -228,7 +235,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         // a tile whose pages have consecutive ids is one box (the run maps walk the pages with a stride
         // of their own): the TMA unit's time goes by the box, not by the byte
         const int first_pi = kbase / ps;
-        bool run = p.page_runs && pages == per_tile && first_pi + per_tile <= p.max_pages && bt[first_pi] >= 0;
+        bool run = p.page_runs && pages == per_tile && first_pi + per_tile <= max_pages && bt[first_pi] >= 0;
         for (int i = 1; run && i < per_tile; ++i) run = bt[first_pi + i] == bt[first_pi] + i;
         if (run) {
           mbar_expect_tx(full, (uint32_t)L::KV_BYTES);
@@ -238,7 +245,7 @@ attention_tc_kernel(const __grid_constant__ CUtensorMap map_k, const __grid_cons
         mbar_expect_tx(full, (uint32_t)(pages * HALVES * ps * 128));
         for (int i = 0; i < pages; ++i) {
           const int pi = first_pi + i;
-          int page = pi < p.max_pages ? bt[pi] : 0;
+          int page = pi < max_pages ? bt[pi] : 0;
           if (page < 0) page = 0;                   // no page lies inside a causal range without a window
           const int y = (page * p.nkv + kvh) * ps;
 #pragma unroll
@@ -629,7 +636,9 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
                                   const int* block_tables, int max_pages, const int* q_start, const int* ctx_len,
                                   const int* tile_seq, const int* tile_row0, int tiles, int row_tiles, int nq, int nkv,
                                   int hd, int page_size, float scale, int num_splits, int tiles_per_split, int total_tokens,
-                                  float* part_o, float* part_lse, int* status, cudaStream_t stream) {
+                                  float* part_o, float* part_lse, const int* seq_row, const int* page_shift, int* status,
+                                  cudaStream_t stream) {
+  SLLM_REQUIRE((seq_row == nullptr) == (page_shift == nullptr), "attention_tc: parts of requests need both their row and their first page");
   SLLM_REQUIRE(row_tiles == 1 || row_tiles == 2, "attention_tc: row_tiles=%d must be 1 or 2", row_tiles);
   SLLM_REQUIRE(num_splits >= 1 && num_splits <= 65535 && tiles_per_split >= 1, "attention_tc: bad context split %d x %d",
                num_splits, tiles_per_split);
@@ -657,7 +666,7 @@ SLLM_EXPORT int sllm_attention_tc(const void* q, const void* k_cache, const void
   p.ctx_len = ctx_len; p.tile_seq = tile_seq; p.tile_row0 = tile_row0; p.status = status; p.max_pages = max_pages;
   p.page_size = page_size; p.nq = nq; p.nkv = nkv; p.scale_log2 = scale * 1.4426950408889634f;
   p.num_splits = num_splits; p.tiles_per_split = num_splits == 1 ? (1 << 30) / TC_BN : tiles_per_split;
-  p.total_tokens = total_tokens; p.part_o = part_o; p.part_lse = part_lse;
+  p.total_tokens = total_tokens; p.part_o = part_o; p.part_lse = part_lse; p.seq_row = seq_row; p.page_shift = page_shift;
   if (row_tiles == 2)
     return hd == 128 ? launch_tc<128, 2>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 2>(mk, mv, rk, rv, p, tiles, stream);
   return hd == 128 ? launch_tc<128, 1>(mk, mv, rk, rv, p, tiles, stream) : launch_tc<64, 1>(mk, mv, rk, rv, p, tiles, stream);

@@ -1220,11 +1220,12 @@ def choose_tc_splits(num_tiles: int, nkv: int, max_ctx: int) -> tuple[int, int]:
 
 
 def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq, nkv, hd, scale, out=None,
-                 row_tiles: int = 1, splits: tuple[int, int] = (1, 0)):
+                 row_tiles: int = 1, splits: tuple[int, int] = (1, 0), parts=None):
     """The prefill form on tcgen05 (tiles of 128 * row_tiles rows, row_tiles 1 or 2; no window; see
     `attention_tiles`).  ``splits`` = (ranges, 64-key tiles a range) cuts the context into ranges
     that run as CTAs of their own and are merged afterwards; ranges x tiles must cover the longest
-    context among the tiles' requests."""
+    context among the tiles' requests.  ``parts`` = (row of ``block_tables``, first page) per sequence of ``q_start`` /
+    ``ctx_len`` when these describe parts of requests (see `block_parts`)."""
     _chk(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles[0], tiles[1])
     if q.dtype != torch.bfloat16 or k_cache.dtype != torch.bfloat16:
         raise KernelError("attention_tc: bfloat16 only")
@@ -1240,11 +1241,45 @@ def attention_tc(q, k_cache, v_cache, block_tables, q_start, ctx_len, tiles, nq,
     call("sllm_attention_tc", _p(q), _p(k_cache), _p(v_cache), k_cache.shape[0], _p(out), _p(block_tables),
          block_tables.shape[1], _p(q_start), _p(ctx_len), _p(tiles[0]), _p(tiles[1]), tiles[2], int(row_tiles), nq, nkv,
          hd, k_cache.shape[2], float(scale), n_splits, max(per, 1), T, _p(part_o), _p(part_lse),
-         _p(_status_word(q.device)), _stream())
+         _p(parts[0]) if parts else None, _p(parts[1]) if parts else None, _p(_status_word(q.device)), _stream())
     if n_splits > 1:
         launches["own"] += 1               # the merge kernel
     _tc_used["since_check"] += 1
     return out
+
+
+def block_parts(q_lens, ctx_lens, group_size: int, block: int, page_size: int, device, rows: int = 128):
+    """Attention inside blocks of positions as ordinary causal attention over parts of requests: a request's portion is
+    cut where it crosses a block's border; a part's keys start at its block's first position, which is the first position
+    of a page (``block`` is a multiple of ``page_size``), so the part reads the request's block table from that page on.
+    Requests of at most 16 (token, head-in-group) rows stay one part each and get no tile (the decode form runs them).
+    Returns ``(q_start, ctx_len, (table_row, first_page), tiles)`` on the device, ``tiles`` as `attention_tiles` gives
+    them for the prefill form, longest first."""
+    starts, ctxs, rows_of, shift = [0], [], [], []
+    tile_s, tile_r, keys = [], [], []
+    for s, (n, c) in enumerate(zip(q_lens, ctx_lens)):
+        pos0 = c - n
+        cuts = [(pos0, c)] if n * group_size <= 16 else \
+            [(max(pos0, b * block), min(c, (b + 1) * block)) for b in range(pos0 // block, (c - 1) // block + 1)]
+        for lo, hi in cuts:
+            first = lo // block * block if n * group_size > 16 else 0
+            if n * group_size > 16:
+                for r0 in range(0, (hi - lo) * group_size, rows):
+                    tile_s.append(len(ctxs))
+                    tile_r.append(r0)
+                    keys.append(lo - first + r0 // group_size)
+            starts.append(starts[-1] + hi - lo)
+            ctxs.append(hi - first)
+            rows_of.append(s)
+            shift.append(first // page_size)
+    order = sorted(range(len(tile_s)), key=lambda i: -keys[i])
+    S = len(ctxs)
+    flat = starts + ctxs + rows_of + shift + [tile_s[i] for i in order] + [tile_r[i] for i in order]
+    t = torch.tensor(flat, dtype=torch.int32).to(device, non_blocking=True)
+    n = len(tile_s)
+    o = S + 1
+    return (t[:o], t[o:o + S], (t[o + S:o + 2 * S], t[o + 2 * S:o + 3 * S]),
+            (t[o + 3 * S:o + 3 * S + n], t[o + 3 * S + n:o + 3 * S + 2 * n], n))
 
 
 @functools.lru_cache(maxsize=4096)
@@ -1265,7 +1300,9 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
         return attention_simt(q, k_cache, v_cache, g.block_tables, step.positions, step.seq_of_token,
                               nq, nkv, hd, scale, window, block)
     G = nq // nkv
-    use_tc = not window and not block and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
+    # blocks that start on page borders: the prefill form runs each block's part of a portion as a causal sequence of its own
+    blocked_tc = bool(block) and block % k_cache.shape[2] == 0 and bool(step.ctx_lens)
+    use_tc = not window and (not block or blocked_tc) and _TC_ATTENTION and tc_attention_supports(hd, k_cache.shape[2])
     key = ("mma", G, nkv, use_tc, block or 0)
     if key not in step.attn_tiles:
         # 128-row CTAs, two per SM.  (The kernel also has a form with two row tiles a CTA, one CTA per SM,
@@ -1282,9 +1319,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
             small_ctx = max((c for c, n in zip(step.ctx_lens, step.q_lens) if n * G <= 16), default=step.max_ctx_len) \
                 if step.ctx_lens else step.max_ctx_len
             splits = choose_splits(small[2], nkv, small_ctx, per_sm, 0 if tma else MMA_MAX_SPLITS)
-        tc_splits = choose_tc_splits(large[2], nkv, step.max_ctx_len) if (large and use_tc) else (1, 0)
-        step.attn_tiles[key] = (small, large, splits, rows, tc_splits)
-    small, large, splits, rows, tc_splits = step.attn_tiles[key]
+        tc_splits = choose_tc_splits(large[2], nkv, step.max_ctx_len) if (large and use_tc and not block) else (1, 0)
+        parts = block_parts(step.q_lens, step.ctx_lens, G, block, k_cache.shape[2], q.device, rows) if (large and use_tc and block) else None
+        step.attn_tiles[key] = (small, large, splits, rows, tc_splits, parts)
+    small, large, splits, rows, tc_splits, parts = step.attn_tiles[key]
     out = torch.empty_like(q)
     if small and tma_attention_supports(hd, k_cache.shape[2]):
         attention_tma_decode(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, splits,
@@ -1292,7 +1330,10 @@ def paged_attention(q, k_cache, v_cache, step, group: int, nq, nkv, hd, scale, w
     elif small:
         attention_mma(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, small, True, splits,
                       nq, nkv, hd, scale, window, out, block)
-    if large and use_tc:
+    if large and use_tc and parts is not None:
+        attention_tc(q, k_cache, v_cache, g.block_tables, parts[0], parts[1], parts[3], nq, nkv, hd, scale, out,
+                     row_tiles=rows // 128, parts=parts[2])
+    elif large and use_tc:
         attention_tc(q, k_cache, v_cache, g.block_tables, step.q_start, step.ctx_len, large, nq, nkv, hd, scale, out,
                      row_tiles=rows // 128, splits=tc_splits)
     elif large:

@@ -48,11 +48,11 @@ CONFIG_A = {
          "mlp": _moe(8, 2, 24, 1.0, groups=(4, 1), shared=32)},
     ],
 }
-CONFIG_B = {          # heads of 64 on pages of 16: the tensor-core attention forms on the GPU (bfloat16); blocks of 50 positions
+CONFIG_B = {          # heads of 64 on pages of 16: the tensor-core attention forms on the GPU (bfloat16); blocks of 48 positions start on page borders
     "architecture": "Nutopel", "vocab": 200, "width": 128, "logit_scale": 1.0, "norm": {"eps": 1e-6},
     "layers": [
         {"type": "gla", "mixer": {"heads": 1, "dim": 64, "vdim": 48, "tau": 4.0, "decay_rank": 8}, "mlp": _moe(4, 2, 64, 2.0, groups=(2, 1))},
-        {"type": "parallel", "mixer": _pair(6, 3, 64, 64, 50, {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 40, "fast": 8.0, "slow": 1.0}},
+        {"type": "parallel", "mixer": _pair(6, 3, 64, 64, 48, {"base": 10000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 40, "fast": 8.0, "slow": 1.0}},
                                             0.125, {"heads": 4, "kv_heads": 1, "dim": 32, "vdim": 32, "conv": 4}), "mlp": _moe(4, 2, 64, 2.0, shared=64)},
         {"type": "parallel", "mixer": _pair(8, 8, 16, 16, 7, {"base": 10000.0, "dims": 8, "scaling": None}, 0.25,
                                             {"heads": 2, "kv_heads": 2, "dim": 64, "vdim": 64, "conv": 4}), "mlp": None},
@@ -298,12 +298,14 @@ def _paged(dev, dtype, nkv, D, ps, lens, rng):
 
 @pytest.mark.parametrize("hd,block,ps,dtype,nq,nkv", [(24, 20, 4, "float32", 4, 2), (64, 50, 16, "bfloat16", 4, 2), (32, 33, 8, "bfloat16", 4, 2),
                                                       (16, 7, 16, "bfloat16", 4, 2), (64, 120, 16, "bfloat16", 6, 1), (128, 64, 32, "bfloat16", 4, 4),
-                                                      (64, 50, 16, "bfloat16", 24, 1), (40, 9, 8, "float32", 3, 1)])
+                                                      (64, 50, 16, "bfloat16", 24, 1), (40, 9, 8, "float32", 3, 1),
+                                                      (64, 48, 16, "bfloat16", 4, 2), (128, 128, 16, "bfloat16", 8, 1), (64, 256, 64, "bfloat16", 2, 2)])
 def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype, nq, nkv):
     """Prompt portions and single decoded tokens whose positions lie at the start, the end and the middle of a block of
     positions, hundreds of tokens into a request.  The key just before the block's start is made to stand out (a copy of
     the query, scaled): were it visible, it would take the whole softmax.  24 heads on one key head are more rows a
-    decoded token than the decode form's tile: its tokens go through the prompt form."""
+    decoded token than the decode form's tile: its tokens go through the prompt form.  Blocks that are whole pages run
+    prompt portions on the tcgen05 form, each block's part of a portion as a causal sequence of its own."""
     import sllm_b200.ops as ops
     if dev == "cpu" and dtype != "float32":
         pytest.skip("the stand-ins are float32")
@@ -586,7 +588,7 @@ def test_keys_at_block_and_page_borders_and_a_long_memory(tmp_path, dev):
         model, _ = build_model(d, dtype, dev)
         tr = traces.Trace()
         at = 0
-        for n in (15, 1, 1, 16, 15, 1, 1, 2, 47, 1, 2, 3, 25):     # up to, onto and over borders of pages (16) and of blocks (50)
+        for n in (15, 1, 1, 16, 14, 1, 1, 2, 45, 1, 2, 3, 25):     # up to, onto and over borders of pages (16) and of blocks (48)
             tr.step([("r0", at, ids[at:at + n], range(n))])
             at += n
         while at < len(ids):
