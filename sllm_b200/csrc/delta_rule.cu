@@ -25,10 +25,11 @@
 //   the gated delta rule (mode 1):  S <- g S;  w = beta (v - S^T k^);  S <- S + k^ w^T;  o = S^T q^
 //       with k^ = k / sqrt(sum(k^2) + 1e-6), q^ likewise times r_scale, beta = sigmoid(b), g = exp(-exp(A) softplus(a + dt))
 //       one number per head.  In terms of the state before the token: S <- g S - (beta g k^)(k^^T S) + k^ (beta v)^T,
-//       so u = k = k^, d = g on every row, a*u = beta g k^, v = beta v, r = q^.  Several value heads may share one
-//       query/key head (head h reads key head h / hdiv).
+//       so u = k = k^, d = g on every row, a*u = beta g k^, v = beta v, r = q^; the walk's own form for this mode reads
+//       the key once and the head's two numbers g and beta g: S <- g S + k^ (beta v - beta g (k^^T S))^T.  Several value
+//       heads may share one query/key head (head h reads key head h / hdiv).
 //   gated linear attention (mode 2):  S <- diag(alpha) S + k v^T;  o = S^T (q r_scale),  alpha = sigmoid(z)^(1/tau) per key
-//       channel: u = a*u = 0, d = alpha.
+//       channel: u = a*u = 0, d = alpha; the walk's form for this mode has no sum before the update.
 //
 // A second kernel finishes the mixer's output: each head's o over its root mean square, times a gain,
 // times sigmoid(gate logit), in the compute dtype.
@@ -149,14 +150,13 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         for (int m = 0; m < PER_LANE; ++m) {
           const int i = lane + 32 * m;
           if (i < DKP) {
-            const bool in = i < dk;
-            const float u = k[q][m] * inv;
-            s_k[tt * DKP + i] = u;
-            s_u[tt * DKP + i] = u;
-            s_au[tt * DKP + i] = beta * g * u;
-            s_d[tt * DKP + i] = in ? g : 0.f;
+            s_k[tt * DKP + i] = k[q][m] * inv;
             s_r[tt * DKP + i] = r[q][m] * rinv;
           }
+        }
+        if (lane == 0) {              // the walk reads the head's two numbers from here (see its mode 1)
+          s_u[tt * DKP] = g;
+          s_u[tt * DKP + 1] = beta * g;
         }
       } else {
 #pragma unroll
@@ -166,8 +166,6 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
             const bool in = i < dk;
             const float z = d[q][m];
             s_k[tt * DKP + i] = k[q][m];
-            s_u[tt * DKP + i] = 0.f;
-            s_au[tt * DKP + i] = 0.f;
             s_d[tt * DKP + i] = in ? expf((fminf(z, 0.f) - log1pf(expf(-fabsf(z)))) * p.inv_tau) : 0.f;
             s_r[tt * DKP + i] = r[q][m] * p.r_scale;
           }
@@ -223,7 +221,7 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
         }
 #pragma unroll
         for (int cc = 0; cc < CB; ++cc) us[cc] = ut[cc] = o[cc] = o2[cc] = 0.f;
-        if (p.mode != 2) {          // (a recurrence without a removal has u = 0: nothing to sum)
+        if (p.mode == 0) {
 #pragma unroll
           for (int n = 0; n < RPT; n += 2) {
             const float ua = u[n * SPLIT], ub = u[(n + 1) * SPLIT];
@@ -239,17 +237,65 @@ __global__ void __launch_bounds__(DR_THREADS) delta_rule_kernel(const DeltaParam
 #pragma unroll
             for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
           }
-        }
 #pragma unroll
-        for (int n = 0; n < RPT; n += 2) {
-          const float ka = k[n * SPLIT], kb = k[(n + 1) * SPLIT], aa = -au[n * SPLIT], ab = -au[(n + 1) * SPLIT];
-          const float da = d[n * SPLIT], db = d[(n + 1) * SPLIT], ra = r[n * SPLIT], rb = r[(n + 1) * SPLIT];
+          for (int n = 0; n < RPT; n += 2) {
+            const float ka = k[n * SPLIT], kb = k[(n + 1) * SPLIT], aa = -au[n * SPLIT], ab = -au[(n + 1) * SPLIT];
+            const float da = d[n * SPLIT], db = d[(n + 1) * SPLIT], ra = r[n * SPLIT], rb = r[(n + 1) * SPLIT];
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+              s[n][cc] = fmaf(ka, vv[cc], fmaf(aa, us[cc], da * s[n][cc]));
+              s[n + 1][cc] = fmaf(kb, vv[cc], fmaf(ab, us[cc], db * s[n + 1][cc]));
+              o[cc] = fmaf(s[n][cc], ra, o[cc]);
+              o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
+            }
+          }
+        } else if (p.mode == 1) {
+          // one decay g and one rate for the whole head, and the key removed is the key written: the token's unit key
+          // is read once and kept, S <- g S + k (beta v - beta g (k^T S))^T.  The loader left g and beta g in the first
+          // two places of the row that holds u in the general form.
+          const float g = b[tt * DKP], bg = b[tt * DKP + 1];
+          float kr[RPT];
+#pragma unroll
+          for (int n = 0; n < RPT; n += 2) {
+            kr[n] = k[n * SPLIT];
+            kr[n + 1] = k[(n + 1) * SPLIT];
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+              us[cc] = fmaf(kr[n], s[n][cc], us[cc]);
+              ut[cc] = fmaf(kr[n + 1], s[n + 1][cc], ut[cc]);
+            }
+          }
 #pragma unroll
           for (int cc = 0; cc < CB; ++cc) {
-            s[n][cc] = fmaf(ka, vv[cc], fmaf(aa, us[cc], da * s[n][cc]));
-            s[n + 1][cc] = fmaf(kb, vv[cc], fmaf(ab, us[cc], db * s[n + 1][cc]));
-            o[cc] = fmaf(s[n][cc], ra, o[cc]);
-            o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
+            us[cc] += ut[cc];
+#pragma unroll
+            for (int w = 1; w < SPLIT; w <<= 1) us[cc] += __shfl_xor_sync(0xffffffffu, us[cc], w);
+            us[cc] = fmaf(-bg, us[cc], vv[cc]);          // what is written along the key
+          }
+#pragma unroll
+          for (int n = 0; n < RPT; n += 2) {
+            const float ra = r[n * SPLIT], rb = r[(n + 1) * SPLIT];
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+              s[n][cc] = fmaf(kr[n], us[cc], g * s[n][cc]);
+              s[n + 1][cc] = fmaf(kr[n + 1], us[cc], g * s[n + 1][cc]);
+              o[cc] = fmaf(s[n][cc], ra, o[cc]);
+              o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
+            }
+          }
+        } else {
+          // no removal: S <- diag(d) S + k v^T
+#pragma unroll
+          for (int n = 0; n < RPT; n += 2) {
+            const float ka = k[n * SPLIT], kb = k[(n + 1) * SPLIT];
+            const float da = d[n * SPLIT], db = d[(n + 1) * SPLIT], ra = r[n * SPLIT], rb = r[(n + 1) * SPLIT];
+#pragma unroll
+            for (int cc = 0; cc < CB; ++cc) {
+              s[n][cc] = fmaf(ka, vv[cc], da * s[n][cc]);
+              s[n + 1][cc] = fmaf(kb, vv[cc], db * s[n + 1][cc]);
+              o[cc] = fmaf(s[n][cc], ra, o[cc]);
+              o2[cc] = fmaf(s[n + 1][cc], rb, o2[cc]);
+            }
           }
         }
         if constexpr (CB == 4) {

@@ -390,7 +390,7 @@ def _portions(dev, lens, slots, cuts, run):
     return {s: np.concatenate(got[s]) for s in lens}
 
 
-CUTS = [(17, 1), (1, 2), (2, 9), (13, 1), (1, 1), (40, 40)]
+CUTS = [(70, 1), (1, 2), (2, 9), (13, 1), (1, 1), (40, 40)]     # (a long first portion: with few heads, the kernel's warp-a-column form)
 
 
 @pytest.mark.parametrize("heads,kv,dk,dv", [(1, 1, 64, 64), (4, 2, 16, 24), (3, 3, 40, 20), (6, 1, 12, 10), (80, 40, 16, 16), (2, 1, 130, 8)])
@@ -411,7 +411,7 @@ def test_gated_delta_rule_in_portions_and_slots(dev, heads, kv, dk, dv):
     mixer = MIXERS.build(PartSpec("gated_delta", {"hidden_size": W, "heads": heads, "kv_heads": kv, "dim": dk, "vdim": dv, "conv": taps, "eps": eps}),
                          dtype=torch.float32, device=dev)
     mixer.bind(lambda rel: torch.from_numpy(w["m." + rel].astype(np.float32)))
-    lens, slots = {0: 37, 1: 21}, {0: 2, 1: 0}
+    lens, slots = {0: 110, 1: 21}, {0: 2, 1: 0}
     xs = {s: rng.standard_normal((n, W)) for s, n in lens.items()}
     want = {s: plain.gated_delta(x, w, "m.", {"heads": heads, "kv_heads": kv, "dim": dk, "vdim": dv}, eps) for s, x in xs.items()}
     cache = LayerCache(states={"delta": torch.zeros((3, heads, dk, dv), dtype=torch.float32, device=dev),
@@ -442,7 +442,7 @@ def test_gated_linear_attention_in_portions_and_slots(dev, heads, dk, dv, tau):
                          dtype=torch.float32, device=dev)
     mixer.bind(lambda rel: torch.from_numpy(w["m." + rel].astype(np.float32)))
     assert mixer.rank == R
-    lens, slots = {0: 37, 1: 21}, {0: 1, 1: 2}
+    lens, slots = {0: 110, 1: 21}, {0: 1, 1: 2}
     xs = {s: rng.standard_normal((n, W)) for s, n in lens.items()}
     want = {s: plain.gated_linear_attention(x, w, "m.", {"heads": heads, "dim": dk, "vdim": dv, "tau": tau}, eps) for s, x in xs.items()}
     cache = LayerCache(states={"gla": torch.zeros((3, heads, dk, dv), dtype=torch.float32, device=dev)})
