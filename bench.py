@@ -416,8 +416,8 @@ def nutopel_config(sz: dict) -> dict:
     dense feed-forward's two thirds)."""
     W, H, D = sz["width"], sz["heads"], sz["dim"]
     mlp = {"kind": "moe", "expert": {"ff": sz["ff"] // 4 // 64 * 64}, "shared": {"ff": sz["ff"] // 2 // 64 * 64},
-           "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}}}
-    gla = {"type": "gla", "mixer": {"heads": W // 64, "dim": 64, "vdim": 64, "tau": 16.0, "decay_rank": 64}, "mlp": mlp}
+           "router": {"experts": 8, "top": 2, "scale": 2.0, "groups": {"count": 4, "keep": 2}}}
+    gla = {"type": "gla", "mixer": {"heads": W // 64, "dim": 64, "vdim": 64, "tau": 8.0, "decay_rank": 64}, "mlp": mlp}
     left = {"heads": H, "kv_heads": max(1, H // 8), "dim": D, "vdim": D, "mask": {"size": 1024}, "scale": D ** -0.5,
             "rot": {"base": 10000.0, "dims": D // 2, "scaling": {"factor": 4.0, "original": 2048, "fast": 32.0, "slow": 1.0}}}
     right = {"heads": W // 128, "kv_heads": max(1, W // 256), "dim": 128, "vdim": 128, "conv": 4}

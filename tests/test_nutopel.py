@@ -63,7 +63,7 @@ ODD = {               # sizes that are multiples of nothing; groups of one exper
     "layers": [
         {"type": "parallel", "mixer": _pair(3, 1, 10, 14, 9, {"base": 50.0, "dims": 6, "scaling": {"factor": 1.5, "original": 16, "fast": 4.0, "slow": 0.5}},
                                             0.4, {"heads": 3, "kv_heads": 3, "dim": 12, "vdim": 10, "conv": 5}), "mlp": _moe(5, 2, 18, 1.1, groups=(5, 3), shared=22)},
-        {"type": "gla", "mixer": {"heads": 5, "dim": 6, "vdim": 10, "tau": 16.0, "decay_rank": 2}, "mlp": _moe(3, 3, 14, 0.5)},
+        {"type": "gla", "mixer": {"heads": 5, "dim": 6, "vdim": 10, "tau": 12.0, "decay_rank": 2}, "mlp": _moe(3, 3, 14, 0.5)},
     ],
 }
 ONLY_GLA = {"architecture": "Nutopel", "vocab": 90, "width": 64, "logit_scale": 2.0, "norm": {"eps": 1e-6},
@@ -297,7 +297,7 @@ def _paged(dev, dtype, nkv, D, ps, lens, rng):
 
 
 @pytest.mark.parametrize("hd,block,ps,dtype,nq,nkv", [(24, 20, 4, "float32", 4, 2), (64, 50, 16, "bfloat16", 4, 2), (32, 33, 8, "bfloat16", 4, 2),
-                                                      (16, 7, 16, "bfloat16", 4, 2), (64, 120, 16, "bfloat16", 6, 1), (128, 64, 32, "bfloat16", 4, 4),
+                                                      (16, 7, 16, "bfloat16", 4, 2), (64, 104, 16, "bfloat16", 6, 1), (128, 64, 32, "bfloat16", 4, 4),
                                                       (64, 50, 16, "bfloat16", 24, 1), (40, 9, 8, "float32", 3, 1),
                                                       (64, 48, 16, "bfloat16", 4, 2), (128, 128, 16, "bfloat16", 8, 1), (64, 256, 64, "bfloat16", 2, 2)])
 def test_a_query_sees_its_own_block_only(dev, hd, block, ps, dtype, nq, nkv):
@@ -427,7 +427,7 @@ def test_gated_delta_rule_in_portions_and_slots(dev, heads, kv, dk, dv):
     assert float(cache.states["delta"][1].abs().max()) == 0.0
 
 
-@pytest.mark.parametrize("heads,dk,dv,tau", [(1, 64, 48, 4.0), (2, 24, 40, 8.0), (5, 6, 10, 16.0), (90, 16, 16, 1.0), (2, 130, 12, 2.0)])
+@pytest.mark.parametrize("heads,dk,dv,tau", [(1, 64, 48, 4.0), (2, 24, 40, 8.0), (5, 6, 10, 12.0), (90, 16, 16, 1.0), (2, 130, 12, 2.0)])
 def test_gated_linear_attention_in_portions_and_slots(dev, heads, dk, dv, tau):
     from sllm_b200.config.plan import PartSpec
     from sllm_b200.parts import MIXERS, LayerCache
@@ -458,7 +458,7 @@ def test_gated_linear_attention_in_portions_and_slots(dev, heads, dk, dv, tau):
 
 
 @pytest.mark.parametrize("E,top,groups,scale", [(6, 3, (3, 2), 1.7), (8, 2, (4, 1), 1.0), (4, 1, None, 0.8), (5, 2, (5, 3), 1.1), (3, 3, None, 0.5),
-                                                (64, 6, (8, 3), 2.5), (16, 4, (2, 2), 1.0)])
+                                                (64, 6, (8, 3), 3.0), (16, 4, (2, 2), 1.0)])
 def test_router_chooses_within_the_best_groups(dev, E, top, groups, scale):
     """The router's kernel against the plain function, with corrections large enough to change the choice (some negative,
     so that an excluded expert's score of zero would win over an allowed one's)."""
