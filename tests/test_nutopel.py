@@ -102,8 +102,9 @@ def plain_logits(d, reqs):
 
 
 def _decided(t):
-    """Corrections two apart, in another order in every layer: which experts a token uses no longer hangs on a close
-    call between two scores (their weights still come from the scores).  bfloat16 rounding moves a router's scores by up
+    """Corrections that are powers of two, in another order in every layer: which experts a token uses no longer hangs on
+    a close call between two scores, nor which groups it keeps on one between two sums of two (sums of two different powers
+    of two differ from one another); the weights still come from the scores.  bfloat16 rounding moves a router's scores by up
     to about 0.01, and with random weights one token in twenty has two experts that close; the token that then goes
     to another expert differs by its whole feed-forward term, which is no fault.  The float32 runs keep the random
     corrections, where the router's every decision counts."""
@@ -111,7 +112,7 @@ def _decided(t):
         if n.endswith("mlp.correction"):
             E = t[n].numel()
             order = np.random.default_rng(E + sum(map(ord, n))).permutation(E)
-            t[n] = torch.from_numpy(order.astype(np.float32) * 2.0)
+            t[n] = torch.from_numpy(2.0 ** (1 + order.astype(np.float32)))
 
 
 def models_for(tmp_path, config, dev, reqs, seed=5, edit=None):
